@@ -21,12 +21,15 @@ class PagedKVSpec:
     """What a mixer that caches keys and values needs: `window` 0 keeps every key, n > 0 only the
     last n positions (the query's own included). `v_head_dim` 0: values have the keys' head size.
     `chunk` n > 0: a query sees only the keys of its own run of n positions counted from 0, so the
-    pages before the run of the next position are never read again."""
+    pages before the run of the next position are never read again. `values_in_keys`: a key row's first
+    `v_head_dim` values are also its value (attention over one cached latent per token), so the layer
+    keeps one tensor and its values are a view into it."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
     chunk: int = 0
+    values_in_keys: bool = False
 
     def first_needed(self, next_pos: int) -> int:
         """The first key that the query at `next_pos`, or any later one, can still see."""

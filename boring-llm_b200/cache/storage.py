@@ -3,8 +3,8 @@
 For every paged group one tensor `[layers in group, 2 (keys, values), pages + 1, kv heads, page size,
 head size]`: the rows of one (page, kv head) lie together, so a kernel reads a page of one head as
 one contiguous tile. A group whose values have another head size than its keys has two tensors instead
-(`[layers in group, pages + 1, kv heads, page size, head size]` each); `keys()` / `values()` give a layer's
-pages either way. For every state group one tensor `[layers in group, request slots, *shape]`.
+(`[layers in group, pages + 1, kv heads, page size, head size]` each), and one whose values are the first
+values of its key rows has the keys' tensor alone; `keys()` / `values()` give a layer's pages either way. For every state group one tensor `[layers in group, request slots, *shape]`.
 Keys are stored after rotation, values as projected (src/model.br:1814-1820).
 """
 from __future__ import annotations
@@ -32,7 +32,14 @@ class CacheStorage:
         self.v_pages: List[torch.Tensor] = []
         for g in manager.paged_groups:
             lead = (manager.num_pages + 1, g.spec.n_kv_heads, manager.page_size)
-            if g.spec.value_dim == g.spec.head_dim:
+            if g.spec.values_in_keys:
+                if g.spec.value_dim > g.spec.head_dim:
+                    raise ValueError(f"values of {g.spec.value_dim} cannot lie inside keys of {g.spec.head_dim}")
+                k = torch.zeros((len(g.cache_layers),) + lead + (g.spec.head_dim,), dtype=kv_dtype, device=self.device)
+                self.kv.append(None)
+                self.k_pages.append(k)
+                self.v_pages.append(k[..., :g.spec.value_dim])
+            elif g.spec.value_dim == g.spec.head_dim:
                 kv = torch.zeros((len(g.cache_layers), 2) + lead + (g.spec.head_dim,), dtype=kv_dtype, device=self.device)
                 self.kv.append(kv)
                 self.k_pages.append(kv[:, 0])
@@ -88,4 +95,5 @@ class CacheStorage:
         return self.state[gi][li]
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self.k_pages + self.v_pages + self.state)
+        own_values = [v for g, v in zip(self.manager.paged_groups, self.v_pages) if not g.spec.values_in_keys]
+        return sum(t.numel() * t.element_size() for t in self.k_pages + own_values + self.state)

@@ -380,6 +380,39 @@ int bl_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, i
                        const int* tile_expert, void* stream);
 int bl_moe_combine_rows(const float* y, const int* pos, const float* wts, float* out, int T, int top, int d, int add, void* stream);
 
+// ids[t, :] = table[tokens[t], :] (table [vocabulary, top] of expert numbers), wts[t, :] = 1 / top (moe.cu).
+int bl_table_route(const int* table, const int* tokens, int T, int top, int* ids, float* wts, void* stream);
+
+// out = table[ids] * scale (elementwise.cu).
+int bl_embed_scaled(const void* table, int table_dtype, const int* ids, float* out, int T, int d, int vocab, float scale, void* stream);
+
+// y[r, c] = glu(kind, x[r, c], x[r, cols + c], limit) on 32-bit sums (norm_gate.cu; the kinds are in common.cuh).
+int bl_glu_act(const float* x, long long ld_x, void* y, int y_dtype, long long ld_y, int rows, int cols, int kind, float limit,
+               void* stream);
+
+// Attention over one cached latent per token (latent.cu). bl_latent_prep: per row of the joined product's 32-bit sums,
+// cq = RMS norm of columns [off_q, off_q + q_rank) times q_norm_w (cq null: skipped), and into the token's page the row
+// [RMS norm of columns [off_kv, off_kv + rank) times kv_norm_w | the next rot_dim columns, the first 2 * rot_half of them
+// rotated in pairs (j, j + rot_half) by float(position) * inv_freq[j], cos and sin times mscale] (cache null: skipped);
+// cache [pages, page_size, rank + rot_dim]. bl_head_gemm_plain: out[t, h, n] = sum_k x[t, h, k] W[h][n, k] (* sigmoid(gate[t, h * N + n])),
+// every operand by its strides in elements. bl_rope_heads: out[t, h, out_off + .] = q[t, h, off + .] (n values, the
+// first 2 * rot_half rotated).
+// bl_latent_attention_plain: q [T, H, dk], out [T, H, dv]: softmax over the visible cached rows (window 0: all) of
+// q . row * scale with an optional sink per head in the denominator, applied to the rows' first dv values.
+int bl_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int rank, int rot_dim, int rot_half, const void* q_norm_w,
+                   int qw_dtype, const void* kv_norm_w, int kw_dtype, float eps, const int* positions, const int* tok_req,
+                   const int* block_table, int max_pages, int page_size, const float* inv_freq, float mscale, void* cq, void* cache,
+                   int dtype, int T, void* stream);
+int bl_head_gemm_plain(const void* x, int x_dtype, long long ldx, long long x_head, const void* w, int w_dtype, long long w_head,
+                       long long w_n, long long w_k, void* out, int out_dtype, long long ld_out, long long out_head, int T, int H,
+                       int N, int K, const float* gate, long long ld_gate, void* stream);
+int bl_rope_heads(const float* q, long long ld, long long head_stride, int off, const int* positions, const float* inv_freq,
+                  int n, int rot_half, float mscale, void* out, int out_dtype, long long ld_out, long long out_head, int out_off, int T,
+                  int H, void* stream);
+int bl_latent_attention_plain(const void* q, const void* cache, int dtype, const int* tok_req, const int* cu_q, const int* ctx_len,
+                              const int* block_table, int max_pages, void* out, int T, int H, int dk, int dv, int page_size,
+                              int window, float scale, const void* sinks, int sink_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

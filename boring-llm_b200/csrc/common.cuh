@@ -58,6 +58,23 @@ __device__ __forceinline__ float bl_silu(float x) { return x / (1.0f + expf(-x))
 // is rounded to bfloat16 (2^-9) anyway and that evaluate it millions of times per step.
 __device__ __forceinline__ float bl_silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
+// Gated activations of a feed-forward, from the gate sum g and the up sum u of one hidden unit:
+//   BL_GLU_SILU       g / (1 + e^-g) * u
+//   BL_GLU_GELU_TANH  0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u
+//   BL_GLU_CLAMPED    g' = min(g, limit), u' = clamp(u, -limit, limit):  g' / (1 + e^(-1.702 g')) * (u' + 1)
+#define BL_GLU_SILU 0
+#define BL_GLU_GELU_TANH 1
+#define BL_GLU_CLAMPED 2
+__device__ __forceinline__ float bl_glu(int kind, float g, float u, float limit) {
+    if (kind == BL_GLU_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g))) * u;
+    if (kind == BL_GLU_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return bl_silu(g) * u;
+}
+
 // What may follow the softmax of an attention row: a sink per head (a learned score whose exponential joins the
 // denominator once, unscaled, with no value) and a gate per (token, head) whose sigmoid multiplies the row's output.
 // bl_attn_tail returns the factor for the row's unnormalised output, given the row's maximum m in the base-2 domain

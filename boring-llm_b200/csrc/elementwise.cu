@@ -36,23 +36,28 @@ extern "C" int bl_device_check(void) {
 // ---------------------------------------------------------------------------------------------
 template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int d) {
+                             float* __restrict__ out, int d, float scale) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int t = blockIdx.x;
     const size_t row = (size_t)ids[t] * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)t * d + i] = bl_load(table + row + i);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[(size_t)t * d + i] = bl_load(table + row + i) * scale;
 }
 
 extern "C" int bl_embed(const void* table, int table_dtype, const int* ids, float* out,
                         int T, int d, int vocab, void* stream) {
+    return bl_embed_scaled(table, table_dtype, ids, out, T, d, vocab, 1.0f, stream);
+}
+
+extern "C" int bl_embed_scaled(const void* table, int table_dtype, const int* ids, float* out,
+                               int T, int d, int vocab, float scale, void* stream) {
     if (T <= 0) return 0;
     if (d <= 0 || vocab <= 0) BL_FAIL("bl_embed: bad sizes d=%d vocab=%d", d, vocab);
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == BL_F32)
-        BL_CUDA(bl_launch_dependent(embed_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)table, ids, out, d));
+        BL_CUDA(bl_launch_dependent(embed_kernel<float>, dim3(T), dim3(128), 0, s, (const float*)table, ids, out, d, scale));
     else if (table_dtype == BL_BF16)
-        BL_CUDA(bl_launch_dependent(embed_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, (const __nv_bfloat16*)table, ids, out, d));
+        BL_CUDA(bl_launch_dependent(embed_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, s, (const __nv_bfloat16*)table, ids, out, d, scale));
     else
         BL_FAIL("bl_embed: unknown table dtype %d", table_dtype);
     BL_CHECK_LAUNCH("bl_embed");

@@ -76,6 +76,17 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const void* __restrict__ 
     }
 }
 
+// Experts chosen by a table over token ids instead of a router: ids[t, :] = table[token[t], :], every weight 1 / top.
+__global__ void table_route_kernel(const int* __restrict__ table, const int* __restrict__ tokens, int T, int top, int* __restrict__ ids,
+                                   float* __restrict__ wts) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= T * top) return;
+    ids[e] = table[(size_t)tokens[e / top] * top + e % top];
+    wts[e] = 1.0f / (float)top;
+}
+
 // out[p, n] = epilogue(x[p / x_div, :] . W[ids[p]][n, :]), one warp per output (the lanes over k, a fixed butterfly):
 // the plain product for rows that each have their own matrix. SWIGLU: W[e] holds N gate rows, then N up rows.
 template <typename TX, typename TW, typename TO, int EPI>
@@ -272,5 +283,13 @@ extern "C" int bl_moe_combine_rows(const float* y, const int* pos, const float* 
     const int blocks = (int)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
     BL_CUDA(bl_launch_dependent(moe_combine_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, y, pos, wts, out, top, d, count, add));
     BL_CHECK_LAUNCH("bl_moe_combine_rows");
+    return 0;
+}
+
+extern "C" int bl_table_route(const int* table, const int* tokens, int T, int top, int* ids, float* wts, void* stream) {
+    if (T <= 0) return 0;
+    if (top <= 0) BL_FAIL("bl_table_route: %d experts a token", top);
+    BL_CUDA(bl_launch_dependent(table_route_kernel, dim3((T * top + 127) / 128), dim3(128), 0, (cudaStream_t)stream, table, tokens, T, top, ids, wts));
+    BL_CHECK_LAUNCH("bl_table_route");
     return 0;
 }

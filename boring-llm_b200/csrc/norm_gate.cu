@@ -327,6 +327,18 @@ __global__ void activation_kernel(const TI* x, TO* y, size_t count, int cols, si
     }
 }
 
+// Gated activations on the 32-bit sums of a joined product: row r holds `cols` gate sums, then `cols` up sums;
+// y[r, c] = bl_glu(kind, gate, up, limit) (common.cuh).
+template <typename TO>
+__global__ void glu_act_kernel(const float* x, TO* y, size_t count, int cols, size_t ld_x, size_t ld_y, int kind, float limit) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / cols, c = e % cols;
+        bl_store(y + r * ld_y + c, bl_glu(kind, x[r * ld_x + c], x[r * ld_x + cols + c], limit));
+    }
+}
+
 // The same, four values a thread: 32-bit rows in, cols and both row strides multiples of 4, 16-byte aligned.
 template <typename TO, int ACT>
 __global__ void activation4_kernel(const float* x, TO* y, size_t count4, int cols4, size_t ld_x, size_t ld_y) {
@@ -419,6 +431,21 @@ extern "C" int bl_depth_mix(const float* streams, long long stride, const void* 
     depth_mix_kernel<<<grid_for((size_t)count, 256), 256, 0, (cudaStream_t)stream>>>(streams, (size_t)stride, coeffs, c_dtype, n,
                                                                                      out, (size_t)count);
     BL_CHECK_LAUNCH("bl_depth_mix");
+    return 0;
+}
+
+extern "C" int bl_glu_act(const float* x, long long ld_x, void* y, int y_dtype, long long ld_y, int rows, int cols, int kind,
+                          float limit, void* stream) {
+    const long long count = (long long)rows * cols;
+    if (count <= 0) return 0;
+    if (ld_x < 2 * (long long)cols || ld_y < cols) BL_FAIL("bl_glu_act: rows of 2 x %d sums are %lld apart, results %lld", cols, ld_x, ld_y);
+    if (kind != BL_GLU_SILU && kind != BL_GLU_GELU_TANH && kind != BL_GLU_CLAMPED) BL_FAIL("bl_glu_act: unknown kind %d", kind);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int g = (int)((count + 255) / 256 < 148 * 16 ? (count + 255) / 256 : 148 * 16);
+    if (y_dtype == BL_F32) BL_CUDA(bl_launch_dependent(glu_act_kernel<float>, dim3(g), dim3(256), 0, s, x, (float*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, kind, limit));
+    else if (y_dtype == BL_BF16) BL_CUDA(bl_launch_dependent(glu_act_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, s, x, (__nv_bfloat16*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, kind, limit));
+    else BL_FAIL("bl_glu_act: unknown dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_glu_act");
     return 0;
 }
 

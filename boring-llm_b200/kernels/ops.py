@@ -123,12 +123,15 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
         raise KernelError(f"{name}: must have shape {tuple(shape)}, got {tuple(t.shape)}")
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] widened to 32-bit. The caller has checked that ids lie inside the table."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] widened to 32-bit (times `scale`). The caller has checked that ids lie inside the table."""
     T = ids.shape[0]
     V, d = table.shape
     _need(table, "table"); _need(ids, "ids", torch.int32, (T,)); _need(out, "out", torch.float32, (T, d))
-    _call(_lib().bl_embed, _p(table), _dt(table), _p(ids), _p(out), T, d, V, _stream())
+    if scale == 1.0:
+        _call(_lib().bl_embed, _p(table), _dt(table), _p(ids), _p(out), T, d, V, _stream())
+    else:
+        _call(_lib().bl_embed_scaled, _p(table), _dt(table), _p(ids), _p(out), T, d, V, ctypes.c_float(scale), _stream())
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -1317,3 +1320,110 @@ def moe_combine_rows(y: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, out:
     if y.shape[1] != d:
         raise KernelError("moe_combine_rows: y and out differ in width")
     _call(_lib().bl_moe_combine_rows, _p(y), _p(pos), _p(wts), _p(out), T, top, d, 1 if add else 0, _stream())
+
+
+GLU_SILU, GLU_GELU_TANH, GLU_CLAMPED = 0, 1, 2
+
+
+def glu_act(sums: torch.Tensor, out: torch.Tensor, kind: int, limit: float = 0.0) -> None:
+    """out[r, c] = glu(sums[r, c], sums[r, N + c]) on the 32-bit sums of a joined gate | up product (N = out's columns):
+    GLU_SILU silu(g) u; GLU_GELU_TANH gelu_tanh(g) u; GLU_CLAMPED g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit)
+    and u' = clamp(u, -limit, limit). Evaluated in 32-bit."""
+    M, N = out.shape
+    ld = _rows32(sums, "sums", M, 2 * N)
+    if out.stride(1) != 1 or not out.is_cuda:
+        raise KernelError("glu_act: out must be a CUDA matrix with contiguous rows")
+    _call(_lib().bl_glu_act, _p(sums), ctypes.c_longlong(ld), _p(out), _dt(out), ctypes.c_longlong(out.stride(0)), M, N, kind,
+          ctypes.c_float(limit), _stream())
+
+
+def table_route(table: torch.Tensor, tokens: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor) -> None:
+    """ids[t] = table[tokens[t]] (table [vocabulary, top] int32), wts[t, :] = 1 / top."""
+    T = tokens.shape[0]
+    top = table.shape[1]
+    _need(table, "table", torch.int32); _need(tokens, "tokens", torch.int32, (T,))
+    _need(ids, "ids", torch.int32, (T, top)); _need(wts, "wts", torch.float32, (T, top))
+    _call(_lib().bl_table_route, _p(table), _p(tokens), T, top, _p(ids), _p(wts), _stream())
+
+
+def latent_prep(proj: torch.Tensor, off_q: int, q_rank: int, off_kv: int, rank: int, rot_dim: int, rot_half: int,
+                q_norm_w: Optional[torch.Tensor], kv_norm_w: Optional[torch.Tensor], eps: float, positions: torch.Tensor,
+                tok_req: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor, mscale: float,
+                cq: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> None:
+    """From the 32-bit sums `proj` of a mixer's joined first product: cq [T, q_rank] = RMS norm of the query latent times
+    its weight (None: skipped), and into each token's page the row [RMS norm of the key/value latent times its weight |
+    the shared key part of rot_dim values, its first 2 * rot_half rotated by the token's position] (`cache` [pages, 1, page,
+    rank + rot_dim]; None: skipped)."""
+    T = proj.shape[0]
+    ld = _rows32(proj, "proj", T, 1)
+    dtype = cq.dtype if cq is not None else cache.dtype
+    page_size = 1
+    if cq is not None:
+        _need(cq, "cq", None, (T, q_rank)); _need(q_norm_w, "q_norm_w", None, (q_rank,))
+    if cache is not None:
+        _need(cache, "cache", dtype); _need(kv_norm_w, "kv_norm_w", None, (rank,))
+        if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != rank + rot_dim:
+            raise KernelError(f"latent_prep: cache {tuple(cache.shape)} does not hold rows of {rank} + {rot_dim}")
+        page_size = cache.shape[2]
+        _need(block_table, "block_table", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    _call(_lib().bl_latent_prep, _p(proj), ld, off_q, q_rank, off_kv, rank, rot_dim, rot_half, _p(q_norm_w), _vec_dt(q_norm_w), _p(kv_norm_w),
+          _vec_dt(kv_norm_w), ctypes.c_float(eps), _p(positions), _p(tok_req), _p(block_table), block_table.shape[1], page_size,
+          _p(inv_freq), ctypes.c_float(mscale), _p(cq), _p(cache), _dt(cq if cq is not None else cache), T, _stream())
+
+
+def _head_view(t: torch.Tensor, name: str, T: int, H: int, n: int):
+    """(row stride, head stride) of a [T, H, >= n] view whose last dimension is contiguous."""
+    if not t.is_cuda or t.dim() != 3 or t.shape[0] != T or t.shape[1] != H or t.shape[2] < n or t.stride(2) != 1:
+        raise KernelError(f"{name}: must be CUDA [T={T}, H={H}, >= {n}] with a contiguous last dimension, got {tuple(t.shape)}")
+    return t.stride(0), t.stride(1)
+
+
+def head_gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """out[t, h, n] = sum_k x[t, h, k] * w[h, n, k] (times sigmoid(gate[t, h * N + n]) if given): a product per head on
+    CUDA cores, one FMA chain per output in ascending k. x [T, H, K] and out [T, H, N] are views with a contiguous last
+    dimension (32-bit or bfloat16), w [H, N, K] a view with any strides; gate 32-bit rows [T, >= H * N]."""
+    T, H, K = x.shape
+    N = w.shape[1]
+    ldx, xh = _head_view(x, "x", T, H, K)
+    ldo, oh = _head_view(out, "out", T, H, N)
+    if w.dim() != 3 or w.shape[0] != H or w.shape[2] != K or not w.is_cuda:
+        raise KernelError(f"head_gemm_plain: w {tuple(w.shape)} does not fit x {tuple(x.shape)}")
+    ld_gate = _rows32(gate, "gate", T, H * N) if gate is not None else 0
+    _call(_lib().bl_head_gemm_plain, _p(x), _dt(x), ctypes.c_longlong(ldx), ctypes.c_longlong(xh), _p(w), _dt(w),
+          ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(w.stride(1)), ctypes.c_longlong(w.stride(2)), _p(out), _dt(out),
+          ctypes.c_longlong(ldo), ctypes.c_longlong(oh), T, H, N, K, _p(gate), ctypes.c_longlong(ld_gate), _stream())
+
+
+def rope_heads(q: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, mscale: float,
+               out: torch.Tensor) -> None:
+    """out[t, h, :] = q[t, h, :] with its first 2 * rot_half values rotated in pairs (j, j + rot_half) by
+    float(position[t]) * inv_freq[j], cos and sin times mscale. q: 32-bit view [T, H, n], out a view of the same shape, last
+    dimensions contiguous."""
+    T, H, n = q.shape
+    if n < 2 * rot_half or q.dtype != torch.float32:
+        raise KernelError("rope_heads: q must be a 32-bit view [T, H, >= 2 * rot_half]")
+    ldq, qh = _head_view(q, "q", T, H, n)
+    ldo, oh = _head_view(out, "out", T, H, n)
+    _need(positions, "positions", torch.int32, (T,)); _need(inv_freq, "inv_freq", torch.float32)
+    _call(_lib().bl_rope_heads, _p(q), ctypes.c_longlong(ldq), ctypes.c_longlong(qh), 0, _p(positions), _p(inv_freq), n, rot_half,
+          ctypes.c_float(mscale), _p(out), _dt(out), ctypes.c_longlong(ldo), ctypes.c_longlong(oh), 0, T, H, _stream())
+
+
+def latent_attention_plain(q: torch.Tensor, cache: torch.Tensor, tok_req: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor,
+                           block_table: torch.Tensor, out: torch.Tensor, window: int, scale: float,
+                           sinks: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of q [T, H, dk] over cached rows of dk values (cache [pages, 1, page, dk]) whose first dv values
+    are also the values: out [T, H, dv]. One warp per (token, head); `window` 0 sees every earlier row; `sinks` [H] joins
+    each head's softmax denominator once."""
+    T, H, dk = q.shape
+    dv = out.shape[2]
+    _need(q, "q", cache.dtype); _need(cache, "cache"); _need(out, "out", q.dtype, (T, H, dv))
+    if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != dk:
+        raise KernelError(f"latent_attention_plain: cache {tuple(cache.shape)} does not hold rows of {dk}")
+    _need(tok_req, "tok_req", torch.int32, (T,)); _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    if sinks is not None:
+        _need(sinks, "sinks", None, (H,))
+    _call(_lib().bl_latent_attention_plain, _p(q), _p(cache), _dt(q), _p(tok_req), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(out), T, H, dk, dv, cache.shape[2], window, ctypes.c_float(scale), _p(sinks), _vec_dt(sinks),
+          _stream())

@@ -4,7 +4,8 @@ from .norm import RMSNorm, LayerNorm
 from .rotary import RotaryTable
 from .attention import Mixer, GQAAttention, GatedSinkAttention, ChunkedTalkingAttention, ParallelMixers
 from .recurrent import GatedLinearAttention, ChannelDeltaRule, MatrixMemory, ShiftedDecayRecurrence
-from .feedforward import FeedForward, SwiGLU, DenseMLP, RoutedExperts
+from .latent import LatentAttention
+from .feedforward import FeedForward, SwiGLU, DenseMLP, RoutedExperts, GluMLP, SumFeedForward, TableExperts
 from .block import PreNormBlock, GatedSandwichBlock, ResidualGate, PostNormBlock
 from .depth import DepthWeightedAverage
 from .embedding import Embedding, OutputHead
@@ -14,5 +15,5 @@ __all__ = ["Part", "StepContext", "StepPlan", "to_device_matrix", "to_device_vec
            "LayerNorm", "RotaryTable", "Mixer", "GQAAttention", "GatedSinkAttention", "GatedLinearAttention",
            "ChannelDeltaRule", "FeedForward", "SwiGLU", "DenseMLP", "PreNormBlock", "GatedSandwichBlock", "ResidualGate",
            "ChunkedTalkingAttention", "ParallelMixers", "MatrixMemory", "ShiftedDecayRecurrence", "RoutedExperts", "PostNormBlock",
-           "DepthWeightedAverage",
+           "DepthWeightedAverage", "LatentAttention", "GluMLP", "SumFeedForward", "TableExperts",
            "Embedding", "OutputHead", "DecoderModel", "LayerCall"]

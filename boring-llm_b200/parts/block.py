@@ -16,29 +16,38 @@ class PreNormBlock(Part):
     """x += mixer(norm1(x)); x += ffn(norm2(x)): sequential residuals around pre-norms, the
     arrangement of the reference's plain layer (src/model.br:1297-1358 with residual_type 0)."""
 
-    def __init__(self, mixer_norm, mixer, ffn_norm, ffn):
+    def __init__(self, mixer_norm, mixer, ffn_norm=None, ffn=None):
+        """A block without a feed-forward (`ffn` None) has only the first of the two."""
         super().__init__()
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("PreNormBlock: a feed-forward and its norm come together")
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
 
     def children(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
 
     def cache_spec(self):
         return self.mixer.cache_spec()
 
     @property
     def graph_safe(self) -> bool:
-        return bool(getattr(self.mixer, "graph_safe", False) and getattr(self.ffn, "graph_safe", False))
+        return bool(getattr(self.mixer, "graph_safe", False) and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
 
     def forward(self, ctx, x, cache_layer: Optional[int], write_cache: bool = True) -> None:
         # a mixer or feed-forward may take the norm in front of it into its first kernel (steps with few rows)
         # (and the product that adds into the stream may begin the norm that reads it next: ctx.next_norm says which,
         # and a part that can finish such a norm says so with `takes_pending_norm`, or, by the step's number of rows,
         # with `takes_pending_norm_at`)
-        ctx.next_norm = self.ffn_norm if takes_pending_norm(self.ffn, x.shape[0]) else None
+        if self.ffn is None:
+            ctx.next_norm = ctx.norm_after_block
+        else:
+            ctx.next_norm = self.ffn_norm if takes_pending_norm(self.ffn, x.shape[0]) else None
         if not self.mixer.forward_fused_norm(ctx, x, self.mixer_norm, cache_layer, write_cache):
             h = self._normed(ctx, self.mixer_norm, x, self.mixer)
             self.mixer.forward(ctx, h, x, cache_layer, write_cache)
+        if self.ffn is None:
+            ctx.next_norm = None
+            return
         ctx.next_norm = ctx.norm_after_block
         if not self.ffn.forward_fused_norm(ctx, x, self.ffn_norm):
             h = self._normed(ctx, self.ffn_norm, x, self.ffn)

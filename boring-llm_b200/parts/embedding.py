@@ -16,11 +16,11 @@ FUSED_MAX_COLUMNS = 16384
 
 class Embedding(Part):
     """x[t] = table[token[t]] (src/model.br:1286-1295; the reference's embedding scale is 1 here),
-    widened to the 32-bit residual stream."""
+    widened to the 32-bit residual stream; `scale` multiplies the rows (in 32-bit)."""
 
-    def __init__(self, vocab: int, dim: int, names: Dict[str, str]):
+    def __init__(self, vocab: int, dim: int, names: Dict[str, str], scale: float = 1.0):
         super().__init__(names)
-        self.vocab, self.dim = vocab, dim
+        self.vocab, self.dim, self.scale = vocab, dim, float(scale)
         self.table: Optional[torch.Tensor] = None
 
     def local_specs(self):
@@ -31,7 +31,7 @@ class Embedding(Part):
 
     def forward(self, ctx, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         x = ctx.empty((ctx.T, self.dim), torch.float32) if out is None else out
-        ops.embed(self.table, ctx.token_ids, x)
+        ops.embed(self.table, ctx.token_ids, x, self.scale)
         return x
 
 

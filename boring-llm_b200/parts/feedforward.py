@@ -6,7 +6,7 @@ from typing import Dict
 import torch
 
 from ..kernels import ops
-from ..weights import TensorSpec, MATRIX, BIAS
+from ..weights import TensorSpec, MATRIX, BIAS, INT_TABLE
 from .base import Part, to_device_matrix
 from .linear import linear, EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU
 
@@ -120,6 +120,75 @@ class SwiGLU(FeedForward):
         linear(ctx, act, self.w_down, residual, None, EPI_RESIDUAL)
 
 
+class GluMLP(FeedForward):
+    """down(glu(gate(h), up(h))), no biases, with the gated activation as an argument:
+
+    * "silu":       silu(g) * u (what `SwiGLU` computes with fused epilogues);
+    * "gelu_tanh":  0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u;
+    * "clamped":    g' = min(g, limit), u' = clamp(u, -limit, limit); g' sigmoid(1.702 g') (u' + 1).
+
+    Gate and up are one joined product over [Wg; Wu] with 32-bit sums; the activation is evaluated on them in 32-bit; the
+    down product adds into the residual stream."""
+    graph_safe = True
+    KINDS = {"silu": ops.GLU_SILU, "gelu_tanh": ops.GLU_GELU_TANH, "clamped": ops.GLU_CLAMPED}
+
+    def __init__(self, dim: int, hidden: int, names: Dict[str, str], activation: str = "silu", limit: float = 0.0):
+        super().__init__(names)
+        if activation not in self.KINDS:
+            raise ValueError(f"GluMLP: activation must be one of {sorted(self.KINDS)}, got {activation!r}")
+        if activation == "clamped" and not limit > 0:
+            raise ValueError(f"GluMLP: the clamped activation needs a positive limit, got {limit}")
+        self.dim, self.hidden, self.activation, self.limit = dim, hidden, activation, float(limit)
+        self.w_gate_up = self.w_down = None
+
+    def local_specs(self):
+        return {"w_gate": TensorSpec((self.hidden, self.dim), MATRIX),
+                "w_up": TensorSpec((self.hidden, self.dim), MATRIX),
+                "w_down": TensorSpec((self.dim, self.hidden), MATRIX)}
+
+    def place(self, local, dtype, device):
+        self.w_gate_up = to_device_matrix(torch.cat([local["w_gate"], local["w_up"]], dim=0), dtype, device)
+        self.w_down = to_device_matrix(local["w_down"], dtype, device)
+
+    def _run(self, ctx, h, out, epilogue):
+        sums = ctx.empty((h.shape[0], 2 * self.hidden), torch.float32)
+        linear(ctx, h, self.w_gate_up, sums, None, EPI_NONE)
+        act = ctx.empty((h.shape[0], self.hidden))
+        ops.glu_act(sums, act, self.KINDS[self.activation], self.limit)
+        linear(ctx, act, self.w_down, out, None, epilogue)
+
+    def forward(self, ctx, h, residual):
+        self._run(ctx, h, residual, EPI_RESIDUAL)
+
+    def apply(self, ctx, h, out):
+        self._run(ctx, h, out, EPI_NONE)
+
+
+class SumFeedForward(FeedForward):
+    """Several feed-forwards that read the same rows; their results are added (routed experts and an expert that every
+    token uses)."""
+
+    def __init__(self, parts):
+        super().__init__()
+        self.parts = list(parts)
+
+    def children(self):
+        return tuple(self.parts)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts)
+
+    def forward(self, ctx, h, residual):
+        for p in self.parts:
+            p.forward(ctx, h, residual)
+
+    def apply(self, ctx, h, out):
+        self.parts[0].apply(ctx, h, out)
+        for p in self.parts[1:]:
+            p.forward(ctx, h, out)
+
+
 class RoutedExperts(FeedForward):
     """A mixture of experts: `n_experts` small SwiGLU feed-forwards without biases, of which each token uses `top`.
 
@@ -128,12 +197,19 @@ class RoutedExperts(FeedForward):
     neighbours; a group's score is the sum of its two largest choice scores, and only experts of the `keep_groups` best
     groups can be chosen. The result is the weighted sum of the chosen experts' outputs, added in the order of the choice.
     The experts' matrices are stacked ([E, 2 * hidden, dim] gate rows then up rows, [E, dim, hidden]); every (token,
-    chosen expert) pair is a row of two products whose rows each use the matrix of their own expert."""
+    chosen expert) pair is a row of two products whose rows each use the matrix of their own expert. `activation` /
+    `limit`: the experts' gated activation, as in `GluMLP` ("silu" is the products' own epilogue, the others a 32-bit pass
+    over the first product's sums)."""
     graph_safe = True
 
     def __init__(self, dim: int, hidden: int, n_experts: int, top: int, names: Dict[str, str], n_groups: int = 1,
-                 keep_groups: int = 1, correction: bool = True):
+                 keep_groups: int = 1, correction: bool = True, activation: str = "silu", limit: float = 0.0):
         super().__init__(names)
+        if activation not in GluMLP.KINDS:
+            raise ValueError(f"experts: activation must be one of {sorted(GluMLP.KINDS)}, got {activation!r}")
+        if activation == "clamped" and not limit > 0:
+            raise ValueError(f"experts: the clamped activation needs a positive limit, got {limit}")
+        self.activation, self.limit = activation, float(limit)
         if n_experts % n_groups != 0 or not 1 <= keep_groups <= n_groups:
             raise ValueError(f"RoutedExperts: {n_experts} experts in {n_groups} groups, {keep_groups} kept")
         if not 1 <= top <= keep_groups * (n_experts // n_groups):
@@ -143,20 +219,28 @@ class RoutedExperts(FeedForward):
         self.router = self.correction = self.w_gate_up = self.w_down = None
         self.record = None               # a list: every step appends a copy of the experts it chose [T, top] (tests; kernels launched singly)
 
-    def local_specs(self):
+    def choice_specs(self):
+        """The tensors that choose a token's experts."""
         s = {"router": TensorSpec((self.E, self.dim), MATRIX)}
         if self.has_correction:
             s["correction"] = TensorSpec((self.E,), BIAS)
+        return s
+
+    def local_specs(self):
+        s = self.choice_specs()
         for e in range(self.E):
             s[f"gate{e}"] = TensorSpec((self.hidden, self.dim), MATRIX)
             s[f"up{e}"] = TensorSpec((self.hidden, self.dim), MATRIX)
             s[f"down{e}"] = TensorSpec((self.dim, self.hidden), MATRIX)
         return s
 
-    def place(self, local, dtype, device):
+    def place_choice(self, local, dtype, device):
         self.router = to_device_matrix(local["router"], dtype, device)
         if self.has_correction:
             self.correction = local["correction"].to(device=device, dtype=torch.float32).contiguous()
+
+    def place(self, local, dtype, device):
+        self.place_choice(local, dtype, device)
         self.w_gate_up = to_device_matrix(torch.stack([torch.cat([local[f"gate{e}"], local[f"up{e}"]], dim=0) for e in range(self.E)]),
                                           dtype, device)
         self.w_down = to_device_matrix(torch.stack([local[f"down{e}"] for e in range(self.E)]), dtype, device)
@@ -182,13 +266,23 @@ class RoutedExperts(FeedForward):
             rows = ctx.empty((row_src.numel(), self.dim))
             ops.gather_rows(h, row_src, self.top, rows)
             act = ctx.empty((row_src.numel(), self.hidden))
-            ops.gemm_grouped(rows, self.w_gate_up, tile_expert, act, EPI_SWIGLU)
+            if self.activation == "silu":
+                ops.gemm_grouped(rows, self.w_gate_up, tile_expert, act, EPI_SWIGLU)
+            else:
+                sums = ctx.empty((row_src.numel(), 2 * self.hidden), torch.float32)
+                ops.gemm_grouped(rows, self.w_gate_up, tile_expert, sums, EPI_NONE)
+                ops.glu_act(sums, act, GluMLP.KINDS[self.activation], self.limit)
             y = ctx.empty((row_src.numel(), self.dim), torch.float32)
             ops.gemm_grouped(act, self.w_down, tile_expert, y, EPI_NONE)
             ops.moe_combine_rows(y, pos, wts, out, add=add)
             return
         act = ctx.empty((T * self.top, self.hidden))
-        ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, act, EPI_SWIGLU)
+        if self.activation == "silu":
+            ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, act, EPI_SWIGLU)
+        else:
+            sums = ctx.empty((T * self.top, 2 * self.hidden), torch.float32)
+            ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, sums, EPI_NONE)
+            ops.glu_act(sums, act, GluMLP.KINDS[self.activation], self.limit)
         y = ctx.empty((T * self.top, self.dim), torch.float32)
         ops.expert_gemm_plain(act, 1, self.w_down, ids, y, EPI_NONE)
         ops.moe_combine(y, wts, out, add=add)
@@ -198,3 +292,38 @@ class RoutedExperts(FeedForward):
 
     def apply(self, ctx, h, out):
         self._run(ctx, h, out, False)
+
+
+class TableExperts(RoutedExperts):
+    """Experts without a router: a table [vocabulary, top] of expert numbers gives every TOKEN ID its experts (the numbers
+    of a row differ), each with weight 1 / top. Everything behind the choice is `RoutedExperts`."""
+
+    def __init__(self, dim: int, hidden: int, n_experts: int, top: int, vocab: int, names: Dict[str, str],
+                 activation: str = "silu", limit: float = 0.0):
+        if not 1 <= top <= n_experts:
+            raise ValueError(f"TableExperts: {top} experts a token out of {n_experts}")
+        super().__init__(dim, hidden, n_experts, top, names, correction=False, activation=activation, limit=limit)
+        self.vocab = vocab
+        self.table = None
+
+    def choice_specs(self):
+        return {"table": TensorSpec((self.vocab, self.top), INT_TABLE, high=self.E)}
+
+    def place_choice(self, local, dtype, device):
+        t = local["table"].to(torch.int64)
+        if int(t.min()) < 0 or int(t.max()) >= self.E:
+            raise ValueError(f"TableExperts: the table names experts outside 0..{self.E - 1}")
+        if self.top > 1:
+            srt = torch.sort(t, dim=1).values
+            if bool((srt[:, 1:] == srt[:, :-1]).any()):
+                raise ValueError("TableExperts: a row of the table names an expert twice")
+        self.table = t.to(device=device, dtype=torch.int32).contiguous()
+
+    def route(self, ctx, h):
+        T = h.shape[0]
+        ids = torch.empty((T, self.top), dtype=torch.int32, device=ctx.device)
+        wts = ctx.empty((T, self.top), torch.float32)
+        ops.table_route(self.table, ctx.token_ids, ids, wts)
+        if self.record is not None:
+            self.record.append(ids.clone())
+        return ids, wts

@@ -26,6 +26,7 @@ class TensorSpec:
     factors); the part that owns the tensor reads it when the tensor is placed."""
     shape: Tuple[int, ...]
     kind: str = MATRIX          # MATRIX | NORM | BIAS | INT_TABLE
+    high: int = 0               # INT_TABLE: the values lie in [0, high) and differ within a row (0: token ids, any)
 
 
 def shape_matches(shape, spec_shape) -> bool:

@@ -128,6 +128,15 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype = t
     for d in spec.shape:
         n *= int(d)
     key = tensor_key(seed, name)
+    if spec.kind == INT_TABLE and spec.high > 0:
+        # numbers below `high` that differ within a row: the row's first is drawn, the others follow it in a ring
+        width = int(spec.shape[-1])
+        if width > spec.high:
+            raise ValueError(f"tensor {name}: rows of {width} different numbers below {spec.high}")
+        h1, _ = _hashes(key, 0, n // width, device)
+        first = (_shr(h1, 1) % int(spec.high)).to(torch.int64)
+        table = (first[:, None] + torch.arange(width, device=device)[None, :]) % int(spec.high)
+        return table.to(torch.int32).reshape(tuple(spec.shape))
     out = torch.empty(n, dtype=torch.int32 if spec.kind == INT_TABLE else dtype, device=device)
     for start in range(0, n, _CHUNK):
         m = min(_CHUNK, n - start)
