@@ -195,7 +195,52 @@ latent_attention_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ c
     }
 }
 
+// tile[i] = i / per: the matrix (head) of each tile of 128 rows when every head has `per` tiles.
+__global__ void head_tiles_kernel(int* __restrict__ tile, int n, int per) {
+    bl_pdl_trigger();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) tile[i] = i / per;
+}
+
+// out[t, h * N + n] = hv[h, t, n] * sigmoid(gate[t, h * N + n]): head-major 32-bit sums back to token rows, gated.
+template <typename TO>
+__global__ void heads_gate_rows_kernel(const float* __restrict__ hv, const float* gate, size_t ld_gate, TO* __restrict__ out, int T, int H,
+                                       int N, size_t Tp) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const size_t total = (size_t)T * H * N;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / ((size_t)H * N), c = e % ((size_t)H * N);
+        const size_t h = c / N, n = c % N;
+        float v = hv[(h * Tp + t) * N + n];
+        if (gate) v *= 1.0f / (1.0f + expf(-gate[t * ld_gate + c]));
+        bl_store(out + e, v);
+    }
+}
+
 }  // namespace
+
+extern "C" int bl_head_tiles(int* tile, int n_heads, int per, void* stream) {
+    if (n_heads <= 0 || per <= 0) BL_FAIL("bl_head_tiles: %d heads with %d tiles each", n_heads, per);
+    const int n = n_heads * per;
+    BL_CUDA(bl_launch_dependent(head_tiles_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, tile, n, per));
+    BL_CHECK_LAUNCH("bl_head_tiles");
+    return 0;
+}
+
+extern "C" int bl_heads_gate_rows(const float* hv, const float* gate, long long ld_gate, void* out, int out_dtype, int T, int H, int N,
+                                  int Tp, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || N <= 0 || Tp < T) BL_FAIL("bl_heads_gate_rows: bad sizes T=%d H=%d N=%d Tp=%d", T, H, N, Tp);
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)T * H * N;
+    const int g = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (out_dtype == BL_F32) BL_CUDA(bl_launch_dependent(heads_gate_rows_kernel<float>, dim3(g), dim3(256), 0, s, hv, gate, (size_t)ld_gate, (float*)out, T, H, N, (size_t)Tp));
+    else if (out_dtype == BL_BF16) BL_CUDA(bl_launch_dependent(heads_gate_rows_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, s, hv, gate, (size_t)ld_gate, (__nv_bfloat16*)out, T, H, N, (size_t)Tp));
+    else BL_FAIL("bl_heads_gate_rows: unknown dtype %d", out_dtype);
+    BL_CHECK_LAUNCH("bl_heads_gate_rows");
+    return 0;
+}
 
 extern "C" int bl_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int rank, int rot_dim, int rot_half,
                               const void* q_norm_w, int qw_dtype, const void* kv_norm_w, int kw_dtype, float eps,

@@ -1,0 +1,318 @@
+// Attention over one cached latent per token on tensor cores (bfloat16 operands, 32-bit scores, softmax and sums).
+// The cache holds rows [latent (rank) | rotated key part (rot)]; the queries have been moved into the latent's space, so
+// every head of every token reads the same rows: keys of dk = rank + rot values whose first `rank` values are the values.
+// Queries and results lie HEAD-MAJOR, [H, Tp, .] with Tp the step's tokens rounded up to the grouped product's tile, so
+// that the products with the heads' own matrices before and after run as one grouped product each.
+//
+// A block is 32 rows and 8 warps. With several new tokens in a request the rows are 32 consecutive tokens of one head;
+// for a request with a single token they are up to 32 of its heads. The block walks the visible keys in blocks of 64,
+// double-buffered through cp.async. Per key block:
+//   scores: warp (row group rg, quarter qt) multiplies its 16 rows by the 16 keys of its quarter over all of dk and
+//           leaves the raw 32-bit scores in shared memory;
+//   values: every warp reads its 16 rows' 64 scores back in fragment layout, runs the online softmax on them (the four
+//           warps of a row group compute the same statistics) and multiplies the weights by its own quarter of the value
+//           columns, up to NTW tiles of 8 columns.
+// Each phase has the tensor-core work split four ways without any product computed twice; the output of 16 rows x 512
+// value columns, which no warp could hold, is 64 registers a thread. A sink per head joins the denominator at the end.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+
+constexpr int PAGE = 16;
+constexpr int KB = 64;            // keys per block
+constexpr int ROWS = 32;          // rows per thread block
+constexpr int THREADS = 256;
+constexpr int PAD = 8;            // bfloat16 elements of padding per shared-memory row (keeps ldmatrix conflict-free)
+constexpr int SROW = KB + 4;      // floats per row of the score buffer
+
+struct LatentParams {
+    const __nv_bfloat16* q_lat; const __nv_bfloat16* q_rot; const __nv_bfloat16* cache; __nv_bfloat16* out;
+    const int* cu_q; const int* ctx_len; const int* block_table; int max_pages;
+    const int* work;              // several tokens: [n][2] (request, first token of a 64-token tile); single: [n] requests
+    int H, Tp, rank, rot, window;
+    float scale_log2;
+    const void* sinks; int sink_dtype;
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(addr), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Keys [key0, key0 + 64) into a stage of rows `row` elements apart. The 16 rows of a page lie together, dk values each.
+// Pages outside [lo, hi] or no longer in the table, and keys past hi, become zeros: they are masked anyway, and zeros keep
+// the value product finite whatever an earlier request left in a page that is used again.
+__device__ __forceinline__ void load_keys(__nv_bfloat16* stage, int row, const LatentParams& p, const int* table, int dk,
+                                          int key0, int lo, int hi) {
+    const int ch = dk / 8;                                        // 16-byte chunks per row
+    for (int i = threadIdx.x; i < KB * ch; i += THREADS) {
+        const int r = i / ch, c = i % ch;
+        const int key = key0 + r;
+        const int first = key - key % PAGE;
+        const int page = (first + PAGE - 1 >= lo && key <= hi) ? table[key / PAGE] : -1;
+        __nv_bfloat16* dst = stage + r * row + c * 8;
+        if (page >= 0) cp_async16(dst, p.cache + ((size_t)page * PAGE + key % PAGE) * dk + c * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+template <int NTW, bool SINGLE>
+__global__ void __launch_bounds__(THREADS, 1)
+latent_attention_mma_kernel(const LatentParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int dk = p.rank + p.rot;
+    const int dkp = (dk + 15) & ~15;
+    const int row = dkp + PAD;
+    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [ROWS][row]
+    __nv_bfloat16* ks = qs + ROWS * row;                                      // [2][KB][row]
+    float* ss = reinterpret_cast<float*>(ks + 2 * KB * row);                  // [ROWS][SROW]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int rg = warp >> 2, qt = warp & 3;
+    const int mi = lane >> 3, ri = lane & 7;                      // ldmatrix: which 8x8 matrix, which row of it
+    bl_pdl_trigger();
+    int r, tok0, head0;
+    if (SINGLE) {
+        const int per = (p.H + ROWS - 1) / ROWS;
+        r = p.work[blockIdx.x / per];
+        tok0 = 0;
+        head0 = (blockIdx.x % per) * ROWS;
+    } else {
+        // all heads of the last tile first: late tiles of a request see the most keys
+        const int unit = gridDim.x / p.H - 1 - blockIdx.x / p.H;
+        r = p.work[2 * (unit >> 1)];
+        tok0 = p.work[2 * (unit >> 1) + 1] + (unit & 1) * ROWS;
+        head0 = blockIdx.x % p.H;
+    }
+    const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
+    const int* table = p.block_table + (size_t)r * p.max_pages;
+    const int n_rows = SINGLE ? (q_len > 0 ? min(ROWS, p.H - head0) : 0) : max(0, min(ROWS, q_len - tok0));
+    if (n_rows <= 0) return;                                      // the whole block leaves together
+    // the padding columns of the operands are zero once and for all (the copies never touch them)
+    for (int i = threadIdx.x; i < (ROWS + 2 * KB) * (row - dk); i += THREADS) {
+        const int rr = i / (row - dk), c = dk + i % (row - dk);
+        qs[rr * row + c] = __float2bfloat16_rn(0.f);
+    }
+    const int p_first = ctx - q_len + tok0;
+    const int p_last = SINGLE ? p_first : p_first + n_rows - 1;
+    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int hi = p_last;
+    const int b_begin = lo / KB, b_end = hi / KB + 1;
+    bl_pdl_wait();                                                // queries and the newest rows of the cache come from kernels before
+    {
+        const int chl = p.rank / 8, ch = dk / 8;
+        for (int i = threadIdx.x; i < ROWS * ch; i += THREADS) {
+            const int rr = i / ch, c = i % ch;
+            __nv_bfloat16* dst = qs + rr * row + c * 8;
+            if (rr < n_rows) {
+                const size_t at = (size_t)(SINGLE ? head0 + rr : head0) * p.Tp + (size_t)(q_begin + (SINGLE ? tok0 : tok0 + rr));
+                const __nv_bfloat16* src = c < chl ? p.q_lat + at * p.rank + c * 8 : p.q_rot + at * p.rot + (c - chl) * 8;
+                cp_async16(dst, src);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    }
+    load_keys(ks, row, p, table, dk, b_begin * KB, lo, hi);
+    cp_async_commit();
+    // rows g and g + 8 of this warp's row group
+    int pos[2], lo_row[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int rr = rg * 16 + g + 8 * h;
+        pos[h] = rr < n_rows ? (SINGLE ? p_first : p_first + rr) : -1;        // a row that is no query sees nothing
+        lo_row[h] = p.window > 0 ? max(0, pos[h] - p.window + 1) : 0;
+    }
+    float o[NTW][4];
+#pragma unroll
+    for (int n = 0; n < NTW; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int v_cols = (p.rank + 15) & ~15;                       // value columns in pairs of tiles
+    for (int b = b_begin; b < b_end; ++b) {
+        __nv_bfloat16* stage = ks + ((b - b_begin) & 1) * KB * row;
+        cp_async_wait_all();
+        __syncthreads();                                          // block b has landed; everybody is through with block b - 1
+        if (b + 1 < b_end) {
+            load_keys(ks + ((b + 1 - b_begin) & 1) * KB * row, row, p, table, dk, (b + 1) * KB, lo, hi);
+            cp_async_commit();
+        }
+        {   // scores of 16 rows x the 16 keys of this warp's quarter
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            for (int kk = 0; kk < dkp / 16; ++kk) {
+                unsigned a[4], bf[4];
+                ldmatrix_x4(a, qs + (rg * 16 + (mi & 1) * 8 + ri) * row + kk * 16 + (mi >> 1) * 8);
+                ldmatrix_x4(bf, stage + (qt * 16 + (mi >> 1) * 8 + ri) * row + kk * 16 + (mi & 1) * 8);
+                mma_bf16(s[0], a, bf[0], bf[1]);
+                mma_bf16(s[1], a, bf[2], bf[3]);
+            }
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                float* d0 = ss + (rg * 16 + g) * SROW + qt * 16 + n * 8 + 2 * t;
+                *reinterpret_cast<float2*>(d0) = make_float2(s[n][0], s[n][1]);
+                *reinterpret_cast<float2*>(d0 + 8 * SROW) = make_float2(s[n][2], s[n][3]);
+            }
+        }
+        __syncthreads();
+        float s[KB / 8][4];
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) {
+            const float* s0 = ss + (rg * 16 + g) * SROW + n * 8 + 2 * t;
+            const float2 u = *reinterpret_cast<const float2*>(s0);
+            const float2 v = *reinterpret_cast<const float2*>(s0 + 8 * SROW);
+            s[n][0] = u.x; s[n][1] = u.y; s[n][2] = v.x; s[n][3] = v.y;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int j = b * KB + n * 8 + 2 * t + (c & 1);
+                const bool seen = j <= pos[c >> 1] && j >= lo_row[c >> 1];
+                s[n][c] = seen ? s[n][c] : -INFINITY;
+                mx[c >> 1] = fmaxf(mx[c >> 1], s[n][c]);
+            }
+        }
+        float m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m[h], mx[h] * p.scale_log2);
+            m_use[h] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen no key yet
+            if (m_new != m[h]) {
+                const float alpha = ex2(m[h] - m_use[h]);         // 2^-inf = 0 on the first block
+                m[h] = m_new;
+                l[h] *= alpha;
+#pragma unroll
+                for (int n = 0; n < NTW; ++n) { o[n][2 * h] *= alpha; o[n][2 * h + 1] *= alpha; }
+            }
+        }
+        float part[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < KB / 8; ++n) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float e = ex2(fmaf(s[n][c], p.scale_log2, -m_use[c >> 1]));     // a masked score is -inf: 2^-inf = 0
+                s[n][c] = e;
+                part[c >> 1] += e;
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            part[h] += __shfl_xor_sync(0xffffffffu, part[h], 1);
+            part[h] += __shfl_xor_sync(0xffffffffu, part[h], 2);
+            l[h] += part[h];
+        }
+        // out += P . V over this warp's value columns, P rounded to bfloat16 as the tensor cores' left operand
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < NTW / 2; ++np) {
+                const int col = (qt * NTW + 2 * np) * 8;
+                if (col < v_cols) {
+                    unsigned bf[4];
+                    ldmatrix_x4_trans(bf, stage + (kk * 16 + (mi & 1) * 8 + ri) * row + col + (mi >> 1) * 8);
+                    mma_bf16(o[2 * np], a, bf[0], bf[1]);
+                    mma_bf16(o[2 * np + 1], a, bf[2], bf[3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int rr = rg * 16 + g + 8 * h;
+        if (rr >= n_rows) continue;
+        const int head = SINGLE ? head0 + rr : head0;
+        float f = 1.f, den = l[h];
+        if (p.sinks) {                                            // one more term of the denominator: unscaled, no value
+            const float sk = bl_load_any(p.sinks, p.sink_dtype, head) * 1.4426950408889634f;
+            const float mm = fmaxf(m[h], sk);
+            f = exp2f(m[h] - mm);
+            den = den * f + exp2f(sk - mm);
+        }
+        const float inv = den > 0.f ? f / den : 0.f;
+        const size_t at = (size_t)head * p.Tp + (size_t)(q_begin + (SINGLE ? tok0 : tok0 + rr));
+        __nv_bfloat16* dst = p.out + at * p.rank;
+#pragma unroll
+        for (int n = 0; n < NTW; ++n) {
+            const int col = (qt * NTW + n) * 8 + 2 * t;
+            if (col < p.rank) *reinterpret_cast<unsigned*>(dst + col) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+        }
+    }
+}
+
+size_t smem_bytes(int dk) {
+    const int row = ((dk + 15) & ~15) + PAD;
+    return (size_t)(ROWS + 2 * KB) * row * sizeof(__nv_bfloat16) + (size_t)ROWS * SROW * sizeof(float);
+}
+
+template <int NTW, bool SINGLE>
+int launch(const LatentParams& p, int blocks, cudaStream_t s) {
+    const size_t bytes = smem_bytes(p.rank + p.rot);
+    static thread_local size_t allowed = 0;
+    if (bytes > allowed) {
+        BL_CUDA(cudaFuncSetAttribute(latent_attention_mma_kernel<NTW, SINGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        allowed = bytes;
+    }
+    BL_CUDA(bl_launch_dependent(latent_attention_mma_kernel<NTW, SINGLE>, dim3(blocks), dim3(THREADS), bytes, s, p));
+    BL_CHECK_LAUNCH("bl_latent_attention_mma");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int bl_latent_attention_mma_supported(int rank, int rot, int page_size) {
+    return page_size == PAGE && rank > 0 && rot >= 0 && rank % 8 == 0 && rot % 8 == 0 && rank <= 512 && smem_bytes(rank + rot) <= 227 * 1024;
+}
+
+extern "C" int bl_latent_attention_mma(const void* q_lat, const void* q_rot, const void* cache, const int* cu_q, const int* ctx_len,
+                                       const int* block_table, int max_pages, const int* work, int n_work, int single, void* out,
+                                       int H, int Tp, int rank, int rot, int page_size, int window, float scale, const void* sinks,
+                                       int sink_dtype, void* stream) {
+    if (n_work <= 0) return 0;
+    if (!bl_latent_attention_mma_supported(rank, rot, page_size))
+        BL_FAIL("bl_latent_attention_mma: rows of %d + %d values in pages of %d are not what this kernel is built for", rank, rot, page_size);
+    if (H <= 0 || Tp <= 0 || max_pages <= 0 || window < 0) BL_FAIL("bl_latent_attention_mma: bad sizes H=%d Tp=%d", H, Tp);
+    if ((((uintptr_t)q_lat | (uintptr_t)q_rot | (uintptr_t)cache | (uintptr_t)out) & 15) != 0)
+        BL_FAIL("bl_latent_attention_mma: queries, cache and output must be 16-byte aligned");
+    LatentParams p;
+    p.q_lat = (const __nv_bfloat16*)q_lat; p.q_rot = (const __nv_bfloat16*)q_rot; p.cache = (const __nv_bfloat16*)cache;
+    p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
+    p.work = work; p.H = H; p.Tp = Tp; p.rank = rank; p.rot = rot; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f; p.sinks = sinks; p.sink_dtype = sink_dtype;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long blocks = single ? (long long)n_work * ((H + ROWS - 1) / ROWS) : (long long)n_work * 2 * H;
+    if (blocks > 0x7fffffffLL) BL_FAIL("bl_latent_attention_mma: too many blocks");
+    const int tiles = (rank + 7) / 8;                             // value tiles of 8 columns, dealt to four warps in even numbers
+    if (tiles <= 16) return single ? launch<4, true>(p, (int)blocks, s) : launch<4, false>(p, (int)blocks, s);
+    if (tiles <= 32) return single ? launch<8, true>(p, (int)blocks, s) : launch<8, false>(p, (int)blocks, s);
+    return single ? launch<16, true>(p, (int)blocks, s) : launch<16, false>(p, (int)blocks, s);
+}

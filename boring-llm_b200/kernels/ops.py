@@ -1427,3 +1427,49 @@ def latent_attention_plain(q: torch.Tensor, cache: torch.Tensor, tok_req: torch.
     _call(_lib().bl_latent_attention_plain, _p(q), _p(cache), _dt(q), _p(tok_req), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(out), T, H, dk, dv, cache.shape[2], window, ctypes.c_float(scale), _p(sinks), _vec_dt(sinks),
           _stream())
+
+
+def latent_attention_mma_supported(dtype: torch.dtype, rank: int, rot: int, page_size: int) -> bool:
+    """Whether the tensor-core kernel takes cached rows of rank + rot values: bfloat16, pages of 16, both parts multiples
+    of 8, values of at most 512, operands that fit shared memory."""
+    return dtype == torch.bfloat16 and bool(_lib().bl_latent_attention_mma_supported(rank, rot, page_size))
+
+
+def latent_attention_mma(q_lat: torch.Tensor, q_rot: Optional[torch.Tensor], cache: torch.Tensor, cu_q: torch.Tensor,
+                         ctx_len: torch.Tensor, block_table: torch.Tensor, work: torch.Tensor, single: bool, out: torch.Tensor,
+                         window: int, scale: float, sinks: Optional[torch.Tensor] = None) -> None:
+    """Causal attention over cached rows [latent | rotated part] on tensor cores. q_lat [H, Tp, rank], q_rot [H, Tp, rot]
+    (None when rot is 0) and out [H, Tp, rank] lie head-major (row h * Tp + t is token t of the step, head h), bfloat16;
+    cache [pages, 1, 16, rank + rot]. `work`: the step's 64-token tiles [n, 2] of requests with several new tokens, or,
+    with `single`, the requests [n] with one. `window` 0 sees every earlier row; `sinks` [H] joins each head's denominator."""
+    H, Tp, rank = q_lat.shape
+    rot = cache.shape[3] - rank
+    _need(q_lat, "q_lat", torch.bfloat16); _need(cache, "cache", torch.bfloat16); _need(out, "out", torch.bfloat16, (H, Tp, rank))
+    if cache.dim() != 4 or cache.shape[1] != 1 or rot < 0:
+        raise KernelError(f"latent_attention_mma: cache {tuple(cache.shape)} does not hold rows of {rank} and more")
+    if rot:
+        _need(q_rot, "q_rot", torch.bfloat16, (H, Tp, rot))
+    _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
+    _need(work, "work", torch.int32)
+    if sinks is not None:
+        _need(sinks, "sinks", None, (H,))
+    _call(_lib().bl_latent_attention_mma, _p(q_lat), _p(q_rot if rot else None), _p(cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(work), work.shape[0], 1 if single else 0, _p(out), H, Tp, rank, rot, cache.shape[2], window,
+          ctypes.c_float(scale), _p(sinks), _vec_dt(sinks), _stream())
+
+
+def head_tiles(n_heads: int, per: int, device) -> torch.Tensor:
+    """[n_heads * per] int32: tile i of a head-major matrix [n_heads, per * 128, .] belongs to head i // per."""
+    tile = torch.empty(n_heads * per, dtype=torch.int32, device=device)
+    _call(_lib().bl_head_tiles, _p(tile), n_heads, per, _stream())
+    return tile
+
+
+def heads_gate_rows(hv: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t, h * N + n] = hv[h, t, n] (* sigmoid(gate[t, h * N + n])): head-major 32-bit sums hv [H, Tp, N] back to the
+    step's token rows out [T, H * N]; gate 32-bit rows [T, >= H * N] that may be a column range of a wider matrix."""
+    H, Tp, N = hv.shape
+    T = out.shape[0]
+    _need(hv, "hv", torch.float32); _need(out, "out", None, (T, H * N))
+    ld = _rows32(gate, "gate", T, H * N) if gate is not None else 0
+    _call(_lib().bl_heads_gate_rows, _p(hv), _p(gate), ctypes.c_longlong(ld), _p(out), _dt(out), T, H, N, Tp, _stream())

@@ -32,8 +32,14 @@ class LatentAttention(Mixer):
     Only [c | rotated part] is cached (one row of kv_rank + rot_dim values per token, `values_in_keys`). The products with
     Uk and Uv are moved to the query's side, q' = Uk_h^T q_nope and out_h = Uv_h (sum_j p_j c_j), so every head of every
     token reads the same cached rows. All of the mixer's first products (Wdq, Wdkv, Wg) are ONE joined product with
-    32-bit sums; both norms, the rotation and the cache write are one kernel; the gate is the epilogue of the product
-    with Uv. Norms, angles, scores and the softmax are 32-bit.
+    32-bit sums; both norms, the rotation and the cache write are one kernel; the gate is applied where the product with
+    Uv is read. Norms, angles, scores and the softmax are 32-bit.
+
+    In bfloat16 (and where the sizes allow: pages of 16, kv_rank, rot_dim and nope_dim multiples of 8, kv_rank <= 512) the
+    part between the two joined products runs head-major: queries, attention results and the products with Uk and Uv
+    lie as [H, Tp, .] with Tp the step's rows rounded up to 128, so that each of the two per-head products is ONE grouped
+    tensor-core product whose tiles take the matrix of their head, and the attention kernel (`ops.latent_attention_mma`)
+    reads and writes that layout. Otherwise, and always in float32, the plain kernels run on token rows.
     """
     graph_safe = True
 
@@ -85,6 +91,8 @@ class LatentAttention(Mixer):
         self.dq_norm = to_device_vector(local["dq_norm"], dtype, device)
         self.wuq = to_device_matrix(local["wuq"], dtype, device)
         self.wuk = to_device_matrix(local["wuk"], dtype, device)              # [H * nope_dim, kv_rank] as stored
+        # Uk_h^T stacked [H, kv_rank, nope_dim]: the matrices of the grouped product that moves the queries into the latent's space
+        self.wuk_t = to_device_matrix(local["wuk"].view(self.H, self.dn, self.rank).transpose(1, 2).contiguous(), dtype, device)
         self.wuv = to_device_matrix(local["wuv"], dtype, device)              # [H * v_dim, kv_rank] as stored
         self.wo = to_device_matrix(local["wo"], dtype, device)
         if self.has_sink:
@@ -114,6 +122,44 @@ class LatentAttention(Mixer):
     def attend(self, ctx, qa, cache, table, out):
         ops.latent_attention_plain(qa, cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, self.window, self.scale, self.sinks)
 
+    def head_major(self, ctx, cache) -> bool:
+        """Whether this step runs on the tensor-core kernels in the head-major layout."""
+        return bool(ctx.fast and self.dn % 8 == 0 and ops.latent_attention_mma_supported(cache.dtype, self.rank, self.dr, cache.shape[2]))
+
+    def _attend_head_major(self, ctx, cq, cache, table, gate, heads):
+        """heads [T, H * v_dim] from the normed query latent cq, over the cached rows, everything in between head-major."""
+        T, H = cq.shape[0], self.H
+        Tp = -(-T // ops.GROUPED_TILE) * ops.GROUPED_TILE
+        key = ("head tiles", H, Tp)
+        if key not in ctx.memo:                       # the same list for every layer of the step with as many heads
+            ctx.memo[key] = ops.head_tiles(H, Tp // ops.GROUPED_TILE, ctx.device)
+        tile_head = ctx.memo[key]
+        q = ctx.empty((T, H * (self.dn + self.dr)), torch.float32)
+        linear(ctx, cq, self.wuq, q, None, EPI_NONE)
+        q3 = q.view(T, H, self.dn + self.dr)
+        qn = ctx.empty((H, Tp, self.dn))
+        ops.rope_heads(q3[:, :, :self.dn], ctx.positions, self.rotary.inv_freq, 0, 1.0, qn.transpose(0, 1)[:T])     # a cast, head-major
+        q_rot = None
+        if self.dr:
+            q_rot = ctx.empty((H, Tp, self.dr))
+            ops.rope_heads(q3[:, :, self.dn:], ctx.positions, self.rotary.inv_freq, self.rotary.rot_half, self.rotary.mscale,
+                           q_rot.transpose(0, 1)[:T])
+        q_lat = ctx.empty((H, Tp, self.rank))
+        ops.gemm_grouped(qn.view(H * Tp, self.dn), self.wuk_t, tile_head, q_lat.view(H * Tp, self.rank), EPI_NONE)
+        lat = ctx.empty((H, Tp, self.rank))
+        plan = ctx.plans.get(PLAN_KEY)
+        if plan is None:                              # a step put together without asking the parts: plan it now
+            plan = attention_plan(ctx.q_lens, ctx.ctx_lens)
+            plan.arrays = {k: torch.from_numpy(v).to(ctx.device) for k, v in plan.arrays.items()}
+            ctx.plans[PLAN_KEY] = plan
+        for work, single in ((plan.arrays["tiles64"], False), (plan.arrays["singles"], True)):
+            if work.shape[0]:
+                ops.latent_attention_mma(q_lat, q_rot, cache, ctx.cu_q, ctx.ctx_len, table, work, single, lat, self.window, self.scale,
+                                         self.sinks)
+        hv = ctx.empty((H, Tp, self.dv), torch.float32)
+        ops.gemm_grouped(lat.view(H * Tp, self.rank), self.wuv.view(H, self.dv, self.rank), tile_head, hv.view(H * Tp, self.dv), EPI_NONE)
+        ops.heads_gate_rows(hv, gate, heads)
+
     def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
         T = h.shape[0]
         if write_cache != self.own_kv:
@@ -125,6 +171,11 @@ class LatentAttention(Mixer):
         ops.latent_prep(proj, 0, self.q_rank, self.off_kv, self.rank, self.dr, self.rotary.rot_half, self.dq_norm, self.dkv_norm,
                         self.eps, ctx.positions, ctx.tok_req, table, self.rotary.inv_freq, self.rotary.mscale, cq,
                         cache if write_cache else None)
+        if self.head_major(ctx, cache):
+            heads = ctx.empty((T, self.H * self.dv))
+            self._attend_head_major(ctx, cq, cache, table, proj[:, self.off_g:] if self.out_gate else None, heads)
+            linear(ctx, heads, self.wo, out, None, epilogue)
+            return
         qa = self.absorbed_queries(ctx, cq)
         lat = ctx.empty((T, self.H, self.rank))
         self.attend(ctx, qa, cache, table, lat)

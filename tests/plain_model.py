@@ -17,7 +17,7 @@ import torch
 
 # ---- reading a model folder (independent of the engine's loader) -----------------------------------
 def read_safetensors(path):
-    """{name: float64 tensor}. Format: 8-byte little-endian header length, JSON header, raw data."""
+    """{name: float64 tensor (int64 for integer tables)}. Format: 8-byte little-endian header length, JSON header, raw data."""
     with open(path, "rb") as f:
         (n,) = struct.unpack("<Q", f.read(8))
         header = json.loads(f.read(n).decode("utf-8"))
@@ -35,6 +35,8 @@ def read_safetensors(path):
             a = u.view(np.float32).astype(np.float64)
         elif e["dtype"] == "F16":
             a = np.frombuffer(raw, dtype="<f2").astype(np.float64)
+        elif e["dtype"] == "I32":                                   # integer tables stay integers
+            a = np.frombuffer(raw, dtype="<i4").astype(np.int64)
         else:
             raise ValueError(f"plain reader: dtype {e['dtype']} of {name}")
         out[name] = torch.from_numpy(a.reshape(e["shape"]).copy())
