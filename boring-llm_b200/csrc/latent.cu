@@ -198,6 +198,7 @@ latent_attention_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ c
 // tile[i] = i / per: the matrix (head) of each tile of 128 rows when every head has `per` tiles.
 __global__ void head_tiles_kernel(int* __restrict__ tile, int n, int per) {
     bl_pdl_trigger();
+    bl_pdl_wait();                    // every kernel of a step waits, or its successor could overtake the kernel before it
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) tile[i] = i / per;
 }

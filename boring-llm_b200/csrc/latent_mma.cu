@@ -113,7 +113,10 @@ latent_attention_mma_kernel(const LatentParams p) {
     const int q_begin = p.cu_q[r], q_len = p.cu_q[r + 1] - q_begin, ctx = p.ctx_len[r];
     const int* table = p.block_table + (size_t)r * p.max_pages;
     const int n_rows = SINGLE ? (q_len > 0 ? min(ROWS, p.H - head0) : 0) : max(0, min(ROWS, q_len - tok0));
-    if (n_rows <= 0) return;                                      // the whole block leaves together
+    if (n_rows <= 0) {                                            // the whole block leaves together
+        bl_pdl_wait();                                            // (a launch whose blocks all left without waiting would let its successor overtake)
+        return;
+    }
     // the padding columns of the operands are zero once and for all (the copies never touch them)
     for (int i = threadIdx.x; i < (ROWS + 2 * KB) * (row - dk); i += THREADS) {
         const int rr = i / (row - dk), c = dk + i % (row - dk);

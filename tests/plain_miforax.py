@@ -49,13 +49,18 @@ def yarn_frequencies(n, base, scaling):
 
 
 def rotate_halves(x, positions, freqs, m):
-    """x [..., T, n] with n = 2 * len(freqs): (u, v) = (x_i, x_(i + n/2)) -> (u cos a - v sin a, v cos a + u sin a),
-    a = position * f_i, cos and sin both times m."""
+    """x [..., T, n] with n >= 2 * len(freqs): the first 2 * len(freqs) values are rotated in pairs (u, v) = (x_i, x_(i + half))
+    -> (u cos a - v sin a, v cos a + u sin a), a = position * f_i, cos and sin both times m; the rest pass unchanged."""
     half = freqs.shape[0]
     a = positions.to(F64)[:, None] * freqs[None, :]
     c, s = torch.cos(a) * m, torch.sin(a) * m
     u, v = x[..., :half], x[..., half:2 * half]
-    return torch.cat([u * c - v * s, v * c + u * s], dim=-1)
+    return torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * half:]], dim=-1)
+
+
+def rotation_of(c):
+    """(f, m) of a mixer: its rot.dims rotated values (rot_dim of them when the key is absent), stretched if it says so."""
+    return yarn_frequencies(c["rot"].get("dims", c["rot_dim"]), c["rot"]["base"], c["rot"].get("scaling"))
 
 
 # ------------------------------------------------------------------------------------------------ attention
@@ -89,7 +94,7 @@ def latent_and_rotated_key(h, w, c, eps, positions):
     r = c["kv_rank"]
     z = h @ w["dkv"].T
     lat = rms_norm(z[:, :r], w["dkv.norm"], eps)
-    f, m = yarn_frequencies(c["rot_dim"], c["rot"]["base"], c["rot"].get("scaling"))
+    f, m = rotation_of(c)
     return lat, rotate_halves(z[:, r:], positions, f, m)
 
 
@@ -99,7 +104,7 @@ def latent_attention_mixer(h, w, c, eps, positions, shared=None):
     H, dn, dr, dv = c["heads"], c["dim"], c["rot_dim"], c["vdim"]
     cq = rms_norm(h @ w["dq"].T, w["dq.norm"], eps)
     q = (cq @ w["uq"].T).view(T, H, dn + dr)
-    f, m = yarn_frequencies(dr, c["rot"]["base"], c["rot"].get("scaling"))
+    f, m = rotation_of(c)
     q_rot = rotate_halves(q[:, :, dn:].permute(1, 0, 2), positions, f, m)            # [H, T, dr]
     lat, k_rot = shared if shared is not None else latent_and_rotated_key(h, w, c, eps, positions)
     k_nope = (lat @ w["uk"].T).view(T, H, dn).permute(1, 0, 2)
