@@ -7,6 +7,7 @@ its roofline.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--sizes 0.5b|3b|7b] [--layers L]
     python bench.py --design fezopel [--sizes 0.5b|3b] [--layers L]     # another design beside Qwen2 at equal sizes (its own JSON line)
     python bench.py --design kavotar [--sizes 0.5b|3b] [--layers L]     # the Kavotar design beside Fezopel and Qwen2 at equal sizes
+    python bench.py --design miforax [--sizes 0.5b|3b] [--layers L]     # the Miforax design beside Fezopel and Qwen2 at equal sizes
 
 One JSON line on standard output. A "step" is one decode step of the whole batch. Requests are real ones: random
 prompts admitted by the scheduler, prefilled in portions through the engine, then decoded; the model comes from the
@@ -391,6 +392,35 @@ def kavotar_config(sizes, n_layers):
                                       "layers": layers, "max_position_embeddings": 32768})
 
 
+MIFORAX_WINDOW = 1024
+MIFORAX_EXPERTS, MIFORAX_TOP = 16, 2
+MIFORAX_LATENT = {"0.5b": (384, 256, 32), "3b": (768, 512, 64), "7b": (1536, 512, 64)}      # query rank, key/value rank, rotated part
+
+
+def miforax_config(sizes, n_layers):
+    """A Miforax model with the width, heads, head size, layers and vocabulary of a Qwen2.5 size: every head has the Qwen2
+    head size unrotated plus a rotated part, values of the head size; every second layer reads the cached rows of the layer
+    before it; windows of 1,024; the first layer has the dense feed-forward, the others 16 experts of a quarter of its
+    hidden size, 2 a token, beside a shared expert of half of it (the dense feed-forward's arithmetic on 4.5 times its weights)."""
+    import boring_llm_b200 as b
+    s = SIZES[sizes]
+    d, H, dh, F, V = (s[k] for k in ("hidden_size", "num_attention_heads", "head_dim", "intermediate_size", "vocab_size"))
+    q_rank, kv_rank, rot = MIFORAX_LATENT[sizes]
+    layers = []
+    for i in range(n_layers):
+        m = {"heads": H, "dim": dh, "rot_dim": rot, "vdim": dh, "q_rank": q_rank, "kv_rank": kv_rank, "scale": (dh + rot) ** -0.5,
+             "mask": {"size": MIFORAX_WINDOW},
+             "rot": {"base": 1000000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        if i % 2 == 1:
+            m["kv_from"] = i - 1
+        mlp = {"kind": "dense", "ff": F} if i == 0 else {
+            "kind": "moe", "expert": {"ff": F // 4 // 8 * 8, "limit": 7.0}, "router": {"experts": MIFORAX_EXPERTS, "top": MIFORAX_TOP},
+            "shared": {"ff": F // 2 // 8 * 8, "limit": 7.0}}
+        layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    return b.MiforaxConfig.from_dict({"architecture": "Miforax", "vocab": V, "width": d, "norm": {"eps": 1e-6},
+                                      "embedding": {"scale": 1.0}, "layers": layers, "max_position_embeddings": 32768})
+
+
 def kernel_time_line(eng, entries, again):
     """The time of every kernel of one step INSIDE its captured graph: the step is captured with a time stamp between
     every two kernels, then `again` (the same shape: it replays that graph) runs, and the stamps of the replay give
@@ -433,13 +463,15 @@ def design_bench(args):
     from boring_llm_b200.engine.runner import StepEntry
     pk = peaks()
     n_layers = args.layers or 8
-    makers = {"fezopel": fezopel_config, "kavotar": kavotar_config,
+    makers = {"fezopel": fezopel_config, "kavotar": kavotar_config, "miforax": miforax_config,
               "qwen2": lambda sizes, n: b.Qwen2Config.from_dict({**COMMON, **SIZES[sizes], "num_hidden_layers": n})}
-    names = ("fezopel", "qwen2") if args.design == "fezopel" else ("kavotar", "fezopel", "qwen2")
+    names = ("fezopel", "qwen2") if args.design == "fezopel" else (args.design, "fezopel", "qwen2")
     out = {"design": args.design, "beside": list(names[1:]), "sizes": args.sizes, "layers": n_layers, "dtype": "bf16", "data": "synthetic",
            "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "peaks": pk["source"], "models": {}}
     if args.design == "fezopel":
         out.update(beside="qwen2", pattern=list(FEZOPEL_PATTERN), window=FEZOPEL_WINDOW)
+    elif args.design == "miforax":
+        out.update(window=MIFORAX_WINDOW, experts=[MIFORAX_EXPERTS, MIFORAX_TOP], latent=list(MIFORAX_LATENT[args.sizes]))
     else:
         out.update(pattern=list(KAVOTAR_PATTERN), chunk=KAVOTAR_CHUNK, experts=[KAVOTAR_EXPERTS, KAVOTAR_TOP, KAVOTAR_GROUPS, KAVOTAR_KEEP])
     clocks = ClockSampler()
@@ -505,7 +537,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "prefill4", "mixed"],
                     help="run one part only and print its figures (for profilers; not the benchmark line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--design", default="", choices=["", "fezopel", "kavotar"],
+    ap.add_argument("--design", default="", choices=["", "fezopel", "kavotar", "miforax"],
                     help="measure another design beside Qwen2 at equal sizes instead of the default workload (its own JSON line)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -415,11 +415,13 @@ int bl_latent_attention_plain(const void* q, const void* cache, int dtype, const
 
 // The same attention on tensor cores (latent_mma.cu): queries q_lat [H, Tp, rank] and q_rot [H, Tp, rot] and the result out
 // [H, Tp, rank] lie head-major, bfloat16; `work` is the step's list of 64-token tiles [n][2] (request, first token) of
-// requests with several new tokens, or, with `single`, the list [n] of requests with one.
+// requests with several new tokens, or, with `single`, the list [n] of requests with one; those may cut their keys into
+// n_splits slices (a block each) that meet in part_o [n * H, n_splits, rank] and part_ml [n * H, n_splits, 2] and a merge kernel.
 int bl_latent_attention_mma_supported(int rank, int rot, int page_size);
 int bl_latent_attention_mma(const void* q_lat, const void* q_rot, const void* cache, const int* cu_q, const int* ctx_len,
                             const int* block_table, int max_pages, const int* work, int n_work, int single, void* out, int H, int Tp,
-                            int rank, int rot, int page_size, int window, float scale, const void* sinks, int sink_dtype, void* stream);
+                            int rank, int rot, int page_size, int window, float scale, const void* sinks, int sink_dtype, int n_splits,
+                            float* part_o, float* part_ml, void* stream);
 // tile[i] = i / per for n_heads * per tiles; out[t, h * N + n] = hv[h, t, n] (* sigmoid(gate[t, h * N + n])) with hv [H, Tp, N] (latent.cu).
 int bl_head_tiles(int* tile, int n_heads, int per, void* stream);
 int bl_heads_gate_rows(const float* hv, const float* gate, long long ld_gate, void* out, int out_dtype, int T, int H, int N, int Tp,

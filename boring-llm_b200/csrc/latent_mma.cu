@@ -33,6 +33,9 @@ struct LatentParams {
     int H, Tp, rank, rot, window;
     float scale_log2;
     const void* sinks; int sink_dtype;
+    // single tokens with a long context: the key blocks are cut into n_splits slices, one block each, which leave their
+    // unnormalised result, maximum and sum here ([requests * H][n_splits][rank] and [..][2]) for the merge kernel
+    float* part_o; float* part_ml; int n_splits;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -84,7 +87,7 @@ __device__ __forceinline__ void load_keys(__nv_bfloat16* stage, int row, const L
 }
 
 template <int NTW, bool SINGLE>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, NTW <= 8 ? 2 : 1)
 latent_attention_mma_kernel(const LatentParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int dk = p.rank + p.rot;
@@ -97,12 +100,15 @@ latent_attention_mma_kernel(const LatentParams p) {
     const int rg = warp >> 2, qt = warp & 3;
     const int mi = lane >> 3, ri = lane & 7;                      // ldmatrix: which 8x8 matrix, which row of it
     bl_pdl_trigger();
-    int r, tok0, head0;
+    int r, tok0, head0, item = 0, split = 0;
     if (SINGLE) {
         const int per = (p.H + ROWS - 1) / ROWS;
-        r = p.work[blockIdx.x / per];
+        const int unit = blockIdx.x / p.n_splits;
+        split = blockIdx.x % p.n_splits;
+        item = unit / per;
+        r = p.work[item];
         tok0 = 0;
-        head0 = (blockIdx.x % per) * ROWS;
+        head0 = (unit % per) * ROWS;
     } else {
         // all heads of the last tile first: late tiles of a request see the most keys
         const int unit = gridDim.x / p.H - 1 - blockIdx.x / p.H;
@@ -126,7 +132,12 @@ latent_attention_mma_kernel(const LatentParams p) {
     const int p_last = SINGLE ? p_first : p_first + n_rows - 1;
     const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
     const int hi = p_last;
-    const int b_begin = lo / KB, b_end = hi / KB + 1;
+    int b_begin = lo / KB, b_end = hi / KB + 1;
+    if (SINGLE && p.n_splits > 1) {
+        const int each = (b_end - b_begin + p.n_splits - 1) / p.n_splits;
+        b_begin = min(b_begin + split * each, b_end);
+        b_end = min(b_begin + each, b_end);
+    }
     bl_pdl_wait();                                                // queries and the newest rows of the cache come from kernels before
     {
         const int chl = p.rank / 8, ch = dk / 8;
@@ -142,7 +153,7 @@ latent_attention_mma_kernel(const LatentParams p) {
             }
         }
     }
-    load_keys(ks, row, p, table, dk, b_begin * KB, lo, hi);
+    if (b_begin < b_end) load_keys(ks, row, p, table, dk, b_begin * KB, lo, hi);
     cp_async_commit();
     // rows g and g + 8 of this warp's row group
     int pos[2], lo_row[2];
@@ -249,6 +260,23 @@ latent_attention_mma_kernel(const LatentParams p) {
             }
         }
     }
+    cp_async_wait_all();                                          // (a slice without key blocks has only asked for its queries)
+    if (SINGLE && p.n_splits > 1) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int rr = rg * 16 + g + 8 * h;
+            if (rr >= n_rows) continue;
+            const size_t prow = ((size_t)item * p.H + head0 + rr) * p.n_splits + split;
+            float* po = p.part_o + prow * p.rank;
+#pragma unroll
+            for (int n = 0; n < NTW; ++n) {
+                const int col = (qt * NTW + n) * 8 + 2 * t;
+                if (col < p.rank) *reinterpret_cast<float2*>(po + col) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+            }
+            if (qt == 0 && t == 0) { p.part_ml[2 * prow] = m[h]; p.part_ml[2 * prow + 1] = l[h]; }
+        }
+        return;
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int rr = rg * 16 + g + 8 * h;
@@ -269,6 +297,37 @@ latent_attention_mma_kernel(const LatentParams p) {
             const int col = (qt * NTW + n) * 8 + 2 * t;
             if (col < p.rank) *reinterpret_cast<unsigned*>(dst + col) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
         }
+    }
+}
+
+// The slices of one (request, head): out = sum_s o_s 2^(m_s - M) / (sum_s l_s 2^(m_s - M) + 2^(sink - M)), in slice order.
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const LatentParams p) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int item = blockIdx.x / p.H, head = blockIdx.x % p.H;
+    const int r = p.work[item];
+    const int q_begin = p.cu_q[r];
+    if (p.cu_q[r + 1] - q_begin <= 0) return;
+    const size_t prow = ((size_t)item * p.H + head) * p.n_splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < p.n_splits; ++s) mm = fmaxf(mm, p.part_ml[2 * (prow + s)]);
+    float sk = -INFINITY;
+    if (p.sinks) { sk = bl_load_any(p.sinks, p.sink_dtype, head) * 1.4426950408889634f; mm = fmaxf(mm, sk); }
+    float den = p.sinks ? exp2f(sk - mm) : 0.f;
+    for (int s = 0; s < p.n_splits; ++s) {
+        const float ms = p.part_ml[2 * (prow + s)];
+        if (ms != -INFINITY) den += p.part_ml[2 * (prow + s) + 1] * exp2f(ms - mm);
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    __nv_bfloat16* dst = p.out + ((size_t)head * p.Tp + q_begin) * p.rank;
+    for (int c = threadIdx.x; c < p.rank; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < p.n_splits; ++s) {
+            const float ms = p.part_ml[2 * (prow + s)];
+            if (ms != -INFINITY) acc += p.part_o[(prow + s) * p.rank + c] * exp2f(ms - mm);
+        }
+        dst[c] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -299,7 +358,7 @@ extern "C" int bl_latent_attention_mma_supported(int rank, int rot, int page_siz
 extern "C" int bl_latent_attention_mma(const void* q_lat, const void* q_rot, const void* cache, const int* cu_q, const int* ctx_len,
                                        const int* block_table, int max_pages, const int* work, int n_work, int single, void* out,
                                        int H, int Tp, int rank, int rot, int page_size, int window, float scale, const void* sinks,
-                                       int sink_dtype, void* stream) {
+                                       int sink_dtype, int n_splits, float* part_o, float* part_ml, void* stream) {
     if (n_work <= 0) return 0;
     if (!bl_latent_attention_mma_supported(rank, rot, page_size))
         BL_FAIL("bl_latent_attention_mma: rows of %d + %d values in pages of %d are not what this kernel is built for", rank, rot, page_size);
@@ -311,11 +370,19 @@ extern "C" int bl_latent_attention_mma(const void* q_lat, const void* q_rot, con
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.work = work; p.H = H; p.Tp = Tp; p.rank = rank; p.rot = rot; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.sinks = sinks; p.sink_dtype = sink_dtype;
+    if (!single || n_splits < 1) n_splits = 1;
+    if (n_splits > 1 && (!part_o || !part_ml)) BL_FAIL("bl_latent_attention_mma: %d slices need scratch memory", n_splits);
+    p.n_splits = n_splits; p.part_o = part_o; p.part_ml = part_ml;
     cudaStream_t s = (cudaStream_t)stream;
-    const long long blocks = single ? (long long)n_work * ((H + ROWS - 1) / ROWS) : (long long)n_work * 2 * H;
+    const long long blocks = single ? (long long)n_work * ((H + ROWS - 1) / ROWS) * n_splits : (long long)n_work * 2 * H;
     if (blocks > 0x7fffffffLL) BL_FAIL("bl_latent_attention_mma: too many blocks");
     const int tiles = (rank + 7) / 8;                             // value tiles of 8 columns, dealt to four warps in even numbers
-    if (tiles <= 16) return single ? launch<4, true>(p, (int)blocks, s) : launch<4, false>(p, (int)blocks, s);
-    if (tiles <= 32) return single ? launch<8, true>(p, (int)blocks, s) : launch<8, false>(p, (int)blocks, s);
-    return single ? launch<16, true>(p, (int)blocks, s) : launch<16, false>(p, (int)blocks, s);
+    int rc;
+    if (tiles <= 16) rc = single ? launch<4, true>(p, (int)blocks, s) : launch<4, false>(p, (int)blocks, s);
+    else if (tiles <= 32) rc = single ? launch<8, true>(p, (int)blocks, s) : launch<8, false>(p, (int)blocks, s);
+    else rc = single ? launch<16, true>(p, (int)blocks, s) : launch<16, false>(p, (int)blocks, s);
+    if (rc || n_splits == 1) return rc;
+    BL_CUDA(bl_launch_dependent(latent_merge_kernel, dim3(n_work * H), dim3(128), 0, s, p));
+    BL_CHECK_LAUNCH("bl_latent_attention_mma (merge)");
+    return 0;
 }

@@ -339,6 +339,29 @@ __global__ void glu_act_kernel(const float* x, TO* y, size_t count, int cols, si
     }
 }
 
+// The gated activations, four hidden units a thread: cols and both row strides multiples of 4, 16-byte aligned rows.
+template <typename TO>
+__global__ void glu_act4_kernel(const float* x, TO* y, size_t count4, int cols4, size_t ld_x, size_t ld_y, int kind, float limit) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count4; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / cols4, c = (e % cols4) * 4;
+        const float4 g = *reinterpret_cast<const float4*>(x + r * ld_x + c);
+        const float4 u = *reinterpret_cast<const float4*>(x + r * ld_x + (size_t)cols4 * 4 + c);
+        const float o0 = bl_glu(kind, g.x, u.x, limit), o1 = bl_glu(kind, g.y, u.y, limit);
+        const float o2 = bl_glu(kind, g.z, u.z, limit), o3 = bl_glu(kind, g.w, u.w, limit);
+        TO* dst = y + r * ld_y + c;
+        if constexpr (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 a = __floats2bfloat162_rn(o0, o1), b = __floats2bfloat162_rn(o2, o3);
+            uint2 v;
+            v.x = *reinterpret_cast<unsigned*>(&a); v.y = *reinterpret_cast<unsigned*>(&b);
+            *reinterpret_cast<uint2*>(dst) = v;
+        }
+    }
+}
+
 // The same, four values a thread: 32-bit rows in, cols and both row strides multiples of 4, 16-byte aligned.
 template <typename TO, int ACT>
 __global__ void activation4_kernel(const float* x, TO* y, size_t count4, int cols4, size_t ld_x, size_t ld_y) {
@@ -441,6 +464,14 @@ extern "C" int bl_glu_act(const float* x, long long ld_x, void* y, int y_dtype, 
     if (ld_x < 2 * (long long)cols || ld_y < cols) BL_FAIL("bl_glu_act: rows of 2 x %d sums are %lld apart, results %lld", cols, ld_x, ld_y);
     if (kind != BL_GLU_SILU && kind != BL_GLU_GELU_TANH && kind != BL_GLU_CLAMPED) BL_FAIL("bl_glu_act: unknown kind %d", kind);
     cudaStream_t s = (cudaStream_t)stream;
+    if (cols % 4 == 0 && ld_x % 4 == 0 && ld_y % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0 && (y_dtype == BL_F32 || y_dtype == BL_BF16)) {
+        const long long count4 = count / 4;
+        const int g4 = (int)((count4 + 255) / 256 < 148 * 16 ? (count4 + 255) / 256 : 148 * 16);
+        if (y_dtype == BL_F32) BL_CUDA(bl_launch_dependent(glu_act4_kernel<float>, dim3(g4), dim3(256), 0, s, x, (float*)y, (size_t)count4, cols / 4, (size_t)ld_x, (size_t)ld_y, kind, limit));
+        else BL_CUDA(bl_launch_dependent(glu_act4_kernel<__nv_bfloat16>, dim3(g4), dim3(256), 0, s, x, (__nv_bfloat16*)y, (size_t)count4, cols / 4, (size_t)ld_x, (size_t)ld_y, kind, limit));
+        BL_CHECK_LAUNCH("bl_glu_act");
+        return 0;
+    }
     const int g = (int)((count + 255) / 256 < 148 * 16 ? (count + 255) / 256 : 148 * 16);
     if (y_dtype == BL_F32) BL_CUDA(bl_launch_dependent(glu_act_kernel<float>, dim3(g), dim3(256), 0, s, x, (float*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, kind, limit));
     else if (y_dtype == BL_BF16) BL_CUDA(bl_launch_dependent(glu_act_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, s, x, (__nv_bfloat16*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, kind, limit));

@@ -1437,11 +1437,12 @@ def latent_attention_mma_supported(dtype: torch.dtype, rank: int, rot: int, page
 
 def latent_attention_mma(q_lat: torch.Tensor, q_rot: Optional[torch.Tensor], cache: torch.Tensor, cu_q: torch.Tensor,
                          ctx_len: torch.Tensor, block_table: torch.Tensor, work: torch.Tensor, single: bool, out: torch.Tensor,
-                         window: int, scale: float, sinks: Optional[torch.Tensor] = None) -> None:
+                         window: int, scale: float, sinks: Optional[torch.Tensor] = None, n_splits: int = 1) -> None:
     """Causal attention over cached rows [latent | rotated part] on tensor cores. q_lat [H, Tp, rank], q_rot [H, Tp, rot]
     (None when rot is 0) and out [H, Tp, rank] lie head-major (row h * Tp + t is token t of the step, head h), bfloat16;
     cache [pages, 1, 16, rank + rot]. `work`: the step's 64-token tiles [n, 2] of requests with several new tokens, or,
-    with `single`, the requests [n] with one. `window` 0 sees every earlier row; `sinks` [H] joins each head's denominator."""
+    with `single`, the requests [n] with one, whose keys `n_splits` blocks may share (slices merged by a second kernel: long
+    contexts in small batches). `window` 0 sees every earlier row; `sinks` [H] joins each head's denominator."""
     H, Tp, rank = q_lat.shape
     rot = cache.shape[3] - rank
     _need(q_lat, "q_lat", torch.bfloat16); _need(cache, "cache", torch.bfloat16); _need(out, "out", torch.bfloat16, (H, Tp, rank))
@@ -1453,9 +1454,26 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: Optional[torch.Tensor], cac
     _need(work, "work", torch.int32)
     if sinks is not None:
         _need(sinks, "sinks", None, (H,))
+    n_splits = max(1, int(n_splits)) if single else 1
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((work.shape[0] * H, n_splits, rank), dtype=torch.float32, device=out.device)
+        part_ml = torch.empty((work.shape[0] * H, n_splits, 2), dtype=torch.float32, device=out.device)
     _call(_lib().bl_latent_attention_mma, _p(q_lat), _p(q_rot if rot else None), _p(cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(work), work.shape[0], 1 if single else 0, _p(out), H, Tp, rank, rot, cache.shape[2], window,
-          ctypes.c_float(scale), _p(sinks), _vec_dt(sinks), _stream())
+          ctypes.c_float(scale), _p(sinks), _vec_dt(sinks), n_splits, _p(part_o), _p(part_ml), _stream())
+
+
+LATENT_ROWS = 32               # rows of a block of the latent attention kernel (heads of a single token)
+LATENT_RESIDENT = 2 * 148      # its blocks that the device holds at once (two an SM up to 256 latent values)
+LATENT_MAX_SPLITS = 16
+
+
+def latent_attention_splits(n_single: int, H: int, longest: int) -> int:
+    """Into how many slices the keys of requests with a single token are cut: as many as fill the device once, one key
+    block of 64 each at least."""
+    units = max(1, n_single * (-(-H // LATENT_ROWS)))
+    return max(1, min(-(-longest // 64), LATENT_RESIDENT // units, LATENT_MAX_SPLITS))
 
 
 def head_tiles(n_heads: int, per: int, device) -> torch.Tensor:

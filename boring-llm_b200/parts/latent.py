@@ -152,10 +152,14 @@ class LatentAttention(Mixer):
             plan = attention_plan(ctx.q_lens, ctx.ctx_lens)
             plan.arrays = {k: torch.from_numpy(v).to(ctx.device) for k, v in plan.arrays.items()}
             ctx.plans[PLAN_KEY] = plan
+        longest = plan.host["longest_single"]
+        if self.window > 0:
+            longest = min(longest, self.window + 64)
         for work, single in ((plan.arrays["tiles64"], False), (plan.arrays["singles"], True)):
             if work.shape[0]:
+                splits = ops.latent_attention_splits(work.shape[0], H, longest) if single else 1
                 ops.latent_attention_mma(q_lat, q_rot, cache, ctx.cu_q, ctx.ctx_len, table, work, single, lat, self.window, self.scale,
-                                         self.sinks)
+                                         self.sinks, splits)
         hv = ctx.empty((H, Tp, self.dv), torch.float32)
         ops.gemm_grouped(lat.view(H * Tp, self.rank), self.wuv.view(H, self.dv, self.rank), tile_head, hv.view(H * Tp, self.dv), EPI_NONE)
         ops.heads_gate_rows(hv, gate, heads)

@@ -347,14 +347,17 @@ def test_latent_attention_kernels(H, rank, rot, window):
         q_lat[:, :T] = dev(q_d[:, :, :rank], dtype).transpose(0, 1)
         q_rot[:, :T] = dev(q_d[:, :, rank:], dtype).transpose(0, 1)
         lat = torch.full((H, Tp, rank), float("nan"), dtype=dtype, device=DEV)
-        for name, single in (("tiles64", False), ("singles", True)):
-            work = torch.from_numpy(plan.arrays[name]).to(DEV)
-            ops.latent_attention_mma(q_lat, q_rot, cache, i32(cu), i32(ctx), table, work, single, lat, window, scale, dev(sinks))
-        got = lat[:, :T].transpose(0, 1).double().cpu()
-        assert torch.isfinite(got).all()
-        err = (got - want).abs().max().item()
-        assert err <= tol * want.abs().max().item(), ("tensor cores", err)
-        assert torch.isnan(lat[:, T:].float()).all()               # rows that are no token of the step are not written
+        for splits in (1, 2, 5):                                   # the single token's keys in one block, in slices, in more slices than key blocks
+            lat.fill_(float("nan"))
+            for name, single in (("tiles64", False), ("singles", True)):
+                work = torch.from_numpy(plan.arrays[name]).to(DEV)
+                ops.latent_attention_mma(q_lat, q_rot, cache, i32(cu), i32(ctx), table, work, single, lat, window, scale, dev(sinks),
+                                         splits)
+            got = lat[:, :T].transpose(0, 1).double().cpu()
+            assert torch.isfinite(got).all()
+            err = (got - want).abs().max().item()
+            assert err <= tol * want.abs().max().item(), ("tensor cores", splits, err)
+            assert torch.isnan(lat[:, T:].float()).all()           # rows that are no token of the step are not written
 
 
 def test_latent_prep_norms_rotation_and_cache_rows():
@@ -391,14 +394,17 @@ def test_latent_prep_norms_rotation_and_cache_rows():
 
 def test_gated_activations_and_the_table_of_experts():
     from boring_llm_b200.kernels import ops
-    sums = rnd(7, 2 * 13, seed=4, scale=2.0)
-    g, u = sums[:, :13], sums[:, 13:]
-    for kind, want in ((ops.GLU_GELU_TANH, pm.gelu_tanh(g) * u),
-                       (ops.GLU_CLAMPED, torch.clamp(g, max=0.8) * torch.sigmoid(1.702 * torch.clamp(g, max=0.8)) * (torch.clamp(u, -0.8, 0.8) + 1.0)),
-                       (ops.GLU_SILU, g * torch.sigmoid(g) * u)):
-        out = torch.empty((7, 13), dtype=torch.float32, device=DEV)
-        ops.glu_act(dev(sums), out, kind, 0.8)
-        assert (out.double().cpu() - want).abs().max() <= 1e-5, kind
+    for n in (13, 24):                                   # a value a thread; four values a thread
+        sums = rnd(7, 2 * n, seed=4, scale=2.0)
+        g, u = sums[:, :n], sums[:, n:]
+        gc = torch.clamp(g, max=0.8)
+        for kind, want in ((ops.GLU_GELU_TANH, pm.gelu_tanh(g) * u),
+                           (ops.GLU_CLAMPED, gc * torch.sigmoid(1.702 * gc) * (torch.clamp(u, -0.8, 0.8) + 1.0)),
+                           (ops.GLU_SILU, g * torch.sigmoid(g) * u)):
+            for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+                out = torch.empty((7, n), dtype=dtype, device=DEV)
+                ops.glu_act(dev(sums), out, kind, 0.8)
+                assert (out.double().cpu() - want).abs().max() <= tol * max(1.0, want.abs().max().item()), (kind, n, dtype)
     table = torch.tensor([[2, 0], [1, 3], [4, 1], [0, 2]], dtype=torch.int32, device=DEV)
     tokens = i32([3, 3, 0, 2, 1])
     ids = torch.empty((5, 2), dtype=torch.int32, device=DEV)
