@@ -415,3 +415,33 @@ def test_gated_activations_and_the_table_of_experts():
     out = torch.empty((5, 8), dtype=torch.float32, device=DEV)
     ops.embed(dev(emb), tokens, out, 2.5)
     assert (out.double().cpu() - emb[tokens.cpu().long()].float().double() * 2.5).abs().max() <= 1e-5
+
+
+def test_the_command_line_and_the_trace_program_on_a_model_folder(folders, tmp_path):
+    """`bin/boring-llm` generates what the plain implementation's arg-max gives, and `bin/trace_run`, started as a user
+    would start it, writes the logits of a mixed trace (float32, and bfloat16 on poisoned pools)."""
+    import os
+    import subprocess
+    import sys
+    folder = folders("A")
+    exe = [sys.executable, os.path.join(helpers.ROOT, "bin", "boring-llm")]
+    prompt = helpers.random_tokens(101, 9, 3)
+    p = subprocess.run(exe + ["--model", folder, "--prompt-tokens", ",".join(map(str, prompt)), "--n-predict", "6", "--dtype", "f32",
+                              "--ctx-size", "64", "--ignore-eos"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr
+    toks = list(prompt)
+    for _ in range(6):
+        toks.append(int(plain_logits(folder, toks)[-1].argmax()))
+    assert p.stdout.strip().splitlines()[-1] == "generated: " + ",".join(map(str, toks[9:]))
+    reqs = {f"t{i}": helpers.random_tokens(101, n, 600 + i) for i, n in enumerate([30, 12, 45])}
+    steps, peak = helpers.mixed_trace(reqs, seed=2, max_live=2)
+    outputs = helpers.run_trace_program(folder, "float32", steps, peak, str(tmp_path / "out"), 101)
+    rows = helpers.collect_rows(steps, outputs)
+    for rid, t in reqs.items():
+        helpers.assert_close(np.stack([rows[(rid, i)] for i in range(len(t))]), plain_logits(folder, t), "float32", rid)
+    outputs = helpers.run_trace_program(folders("A", 0.1), "bfloat16", steps, peak, str(tmp_path / "out16"), 101, extra=["--poison"])
+    rows = helpers.collect_rows(steps, outputs)
+    for rid, t in reqs.items():
+        got = np.stack([rows[(rid, i)] for i in range(len(t))])
+        want = plain_logits(folders("A", 0.1), t)
+        assert np.isfinite(got).all() and np.median(np.abs(got - want).max(-1)) <= BF16_TOL / 4 * np.abs(want).max(), rid
