@@ -20,7 +20,9 @@ int bl_rmsnorm(const float* x, const int* row_idx, const void* w, int w_dtype, v
                int rows, int d, float eps, void* stream);
 
 // Plain matrix product on CUDA cores, 32-bit accumulation in ascending k for every output element:
-// out[M, N] = epilogue(x[M, K] . W[N, K]^T). For BL_EPI_SWIGLU W has 2N rows (gate, then up).
+// out[M, N] = epilogue(x[M, K] . W[N, K]^T). For BL_EPI_SWIGLU W has 2N rows (gate, then up), and `bias`, which that epilogue
+// does not add, may point to two 32-bit numbers {kind, limit} on the device that name the gated activation (BL_GLU_* of
+// common.cuh; null: SiLU). The same holds for every product below that takes a bias and this epilogue.
 int bl_gemm_plain(const void* x, int x_dtype, const void* w, int w_dtype, const void* bias, int bias_dtype,
                   void* out, int out_dtype, int M, int N, int K, int epilogue, void* stream);
 
@@ -363,11 +365,12 @@ int bl_attention_decode_talk(const void* q, const void* k_cache, const void* v_c
 // none); experts in n_groups runs of neighbours, a group's score the sum of its two largest choice scores, the `keep` best
 // groups stay open; ids [T, top] the `top` largest choice scores among them in descending order, wts [T, top] their s.
 // bl_expert_gemm_plain: out[p, :] = epilogue(x[p / x_div, :] . W[ids[p]]^T), W[e] = w + e * expert_stride elements
-// ([N, K], or [2N, K] gate rows then up rows for BL_EPI_SWIGLU). bl_moe_combine: out[t, :] = (add ? out[t, :] : 0) + sum_k wts[t, k] y[t * top + k, :].
+// ([N, K], or [2N, K] gate rows then up rows for BL_EPI_SWIGLU, whose gated activation `act` names: {kind, limit} on the
+// device, null for SiLU). bl_moe_combine: out[t, :] = (add ? out[t, :] : 0) + sum_k wts[t, k] y[t * top + k, :].
 int bl_moe_route(const float* z, int ldz, const void* correction, int corr_dtype, int T, int E, int top, int n_groups, int keep,
                  int* ids, float* wts, void* stream);
 int bl_expert_gemm_plain(const void* x, int x_dtype, int x_div, const void* w, int w_dtype, long long expert_stride, const int* ids,
-                         void* out, int out_dtype, int P, int N, int K, int epilogue, void* stream);
+                         void* out, int out_dtype, int P, int N, int K, int epilogue, const float* act, void* stream);
 int bl_moe_combine(const float* y, const float* wts, float* out, int T, int top, int d, int add, void* stream);
 // The same on tensor cores: the pairs (token, chosen expert) are laid out expert by expert in tiles of `tile` rows
 // (bl_moe_plan: pos [P] the row of each pair, row_src [max_tiles * tile] the pair of each row or -1, tile_expert
@@ -377,7 +380,7 @@ int bl_moe_combine(const float* y, const float* wts, float* out, int T, int top,
 int bl_moe_plan(const int* ids, int P, int E, int tile, int max_tiles, int* pos, int* row_src, int* tile_expert, void* stream);
 int bl_gather_rows(const void* x, const int* row_src, int div, void* dst, int rows, int cols, void* stream);
 int bl_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int epilogue, int n_experts,
-                       const int* tile_expert, void* stream);
+                       const int* tile_expert, const float* act, void* stream);
 int bl_moe_combine_rows(const float* y, const int* pos, const float* wts, float* out, int T, int top, int d, int add, void* stream);
 
 // ids[t, :] = table[tokens[t], :] (table [vocabulary, top] of expert numbers), wts[t, :] = 1 / top (moe.cu).

@@ -74,6 +74,30 @@ __device__ __forceinline__ float bl_glu(int kind, float g, float u, float limit)
     }
     return bl_silu(g) * u;
 }
+// The gated epilogue of a product (BL_EPI_SWIGLU) computes silu(gate) * up unless the product's `bias` argument, which
+// that epilogue does not use otherwise, points to two 32-bit numbers {kind, limit}: then bl_glu(kind, gate, up, limit).
+// bl_glu_fast: the same with the fast exponential and division of bl_silu_fast, for epilogues that round to bfloat16
+// (0.5 g (1 + tanh(z)) = g / (1 + e^(-2z)), so each form is one exponential and one division).
+__device__ __forceinline__ float bl_glu_fast(int kind, float g, float u, float limit) {
+    if (kind == BL_GLU_GELU_TANH)
+        return __fdividef(g, 1.0f + __expf(-1.59576912160573071176f * (g + 0.044715f * g * g * g))) * u;
+    if (kind == BL_GLU_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+struct BlGluArgs { int kind; float limit; };
+__device__ __forceinline__ BlGluArgs bl_glu_args(const void* two_numbers) {
+    BlGluArgs a{BL_GLU_SILU, 0.f};
+    if (two_numbers != nullptr) {
+        const float* f = reinterpret_cast<const float*>(two_numbers);
+        a.kind = (int)f[0];
+        a.limit = f[1];
+    }
+    return a;
+}
 
 // What may follow the softmax of an attention row: a sink per head (a learned score whose exponential joins the
 // denominator once, unscaled, with no value) and a gate per (token, head) whose sigmoid multiplies the row's output.

@@ -60,6 +60,7 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
         }
         __syncthreads();
     }
+    const BlGluArgs glu = bl_glu_args(EPI == BL_EPI_SWIGLU ? bias : nullptr);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int m = m0 + ty * 4 + i;
@@ -72,7 +73,7 @@ gemm_plain_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const void
             float v = acc[i][j];
             if (EPI == BL_EPI_BIAS) v += bl_load_any(bias, bias_dtype, n);
             if (EPI == BL_EPI_RESIDUAL) v += bl_load(dst);
-            if (EPI == BL_EPI_SWIGLU) v = bl_silu(v) * acu[i][j];
+            if (EPI == BL_EPI_SWIGLU) v = bl_glu(glu.kind, v, acu[i][j], glu.limit);
             if (EPI == BL_EPI_DECAY) {                 // exp(-coef[head] * softplus(sign * (acc + bias))), head = n / group
                 if (bias) v += bl_load_any(bias, bias_dtype, n);
                 const float u = sign * v;

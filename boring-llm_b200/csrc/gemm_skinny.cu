@@ -204,6 +204,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
     }
     // the first COLS * TOK threads each own one output element (their residual or bias is already in a register)
     // (every lane of a warp makes the same number of trips: COLS * TOK is a multiple of 32)
+    const BlGluArgs glu = bl_glu_args(GLU ? bias : nullptr);
     for (int i = threadIdx.x; i < COLS * TOK; i += NW * 32) {
         const int c = i % COLS, tok = i / COLS;
         const int n = n0 + c, m = m0 + tok;
@@ -216,7 +217,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x /* written by the kernel before: no re
             if (lk.ss_in != nullptr) { const float r = row_scale[tok]; v *= r; if (GLU) u *= r; }
             TO* dst = out + (size_t)m * N + n;
             if (EPI == BL_EPI_BIAS || EPI == BL_EPI_RESIDUAL) v += (i == threadIdx.x) ? e_add : (EPI == BL_EPI_BIAS ? bl_load_any(bias, bias_dtype, n) : bl_load(dst));
-            if (GLU) v = bl_silu(v) * u;
+            if (GLU) v = bl_glu(glu.kind, v, u, glu.limit);
             bl_store(dst, v);
         }
         if (begins_norm) {                                        // (the same for the whole block)

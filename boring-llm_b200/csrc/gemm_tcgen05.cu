@@ -163,6 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int r_sub = lane >> 3, c4 = (lane & 7) * 4;                       // this lane's row (of four) and column quad when writing out
         const bool vec_ok = (N % 4) == 0;
         constexpr int CHUNKS = GLU ? 2 : BN / 32;
+        const BlGluArgs glu = bl_glu_args(GLU ? bias : nullptr);
 #pragma unroll 1
         for (int c = 0; c < CHUNKS; ++c) {
             uint32_t r[32];
@@ -172,7 +173,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld32(lane_addr + 64 + c * 32, u);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu_fast(__uint_as_float(r[j])) * __uint_as_float(u[j]));
+                for (int j = 0; j < 32; ++j) {
+                    const float g1 = __uint_as_float(r[j]), u1 = __uint_as_float(u[j]);
+                    r[j] = __float_as_uint(bl_glu_fast(glu.kind, g1, u1, glu.limit));
+                }
             } else {
                 tmem_ld_wait();
             }
@@ -303,9 +307,10 @@ extern "C" int bl_gemm_tc(const void* x, const void* w, const void* bias, int bi
 
 // The grouped product: x [M, K] lies in tiles of 128 rows, tile i belonging to matrix tile_expert[i] (negative: the tile is
 // empty and skipped) of the stack w [n_experts, N, K] ([n_experts, 2N, K], gate rows then up rows, for BL_EPI_SWIGLU);
-// out [M, N] = epilogue(x . W[expert of the row's tile]^T). M a multiple of 128; epilogues BL_EPI_NONE and BL_EPI_SWIGLU.
+// out [M, N] = epilogue(x . W[expert of the row's tile]^T). M a multiple of 128; epilogues BL_EPI_NONE and BL_EPI_SWIGLU,
+// the latter with the gated activation that `act` ({kind, limit} on the device, null: SiLU) names.
 extern "C" int bl_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int epilogue,
-                                  int n_experts, const int* tile_expert, void* stream) {
+                                  int n_experts, const int* tile_expert, const float* act, void* stream) {
     if (M <= 0) return 0;
     if (N <= 0 || K <= 0 || n_experts <= 0 || M % BM != 0 || tile_expert == nullptr)
         BL_FAIL("bl_gemm_tc_grouped: bad sizes M=%d N=%d K=%d experts=%d", M, N, K, n_experts);
@@ -320,8 +325,8 @@ extern "C" int bl_gemm_tc_grouped(const void* x, const void* w, void* out, int o
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == BL_F32 && epilogue == BL_EPI_NONE) return launch<BL_EPI_NONE, float>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
     if (out_dtype == BL_BF16 && epilogue == BL_EPI_NONE) return launch<BL_EPI_NONE, __nv_bfloat16>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
-    if (out_dtype == BL_BF16 && glu) return launch<BL_EPI_SWIGLU, __nv_bfloat16>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
-    if (out_dtype == BL_F32 && glu) return launch<BL_EPI_SWIGLU, float>(a, b, nullptr, 0, out, M, N, K, s, tile_expert, expert_rows);
+    if (out_dtype == BL_BF16 && glu) return launch<BL_EPI_SWIGLU, __nv_bfloat16>(a, b, act, BL_F32, out, M, N, K, s, tile_expert, expert_rows);
+    if (out_dtype == BL_F32 && glu) return launch<BL_EPI_SWIGLU, float>(a, b, act, BL_F32, out, M, N, K, s, tile_expert, expert_rows);
     BL_FAIL("bl_gemm_tc_grouped: epilogue %d with output dtype %d is not built", epilogue, out_dtype);
 }
 

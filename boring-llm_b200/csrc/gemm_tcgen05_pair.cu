@@ -371,6 +371,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!mbar_wait(acc_full0 + 8 * buf, (local / 2) & 1, give_up, 3)) break;
             fence_after_sync();
             const uint32_t lane_addr = tmem + buf * 256 + ((uint32_t)(quarter * 32) << 16);
+            const BlGluArgs glu = bl_glu_args(GLU ? bias : nullptr);
 #pragma unroll 1
             for (int c = half; c < CHUNKS; c += 2) {
                 uint32_t r[32];
@@ -380,7 +381,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld32(lane_addr + BN / 2 + c * 32, u);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu_fast(__uint_as_float(r[j]) * row_scale) * (__uint_as_float(u[j]) * row_scale));
+                    for (int j = 0; j < 32; ++j) {
+                        const float g1 = __uint_as_float(r[j]) * row_scale, u1 = __uint_as_float(u[j]) * row_scale;
+                        r[j] = __float_as_uint(bl_glu_fast(glu.kind, g1, u1, glu.limit));
+                    }
                 } else {
                     tmem_ld_wait();
                 }

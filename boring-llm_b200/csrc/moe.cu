@@ -92,7 +92,7 @@ __global__ void table_route_kernel(const int* __restrict__ table, const int* __r
 template <typename TX, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(WARPS * 32)
 expert_gemm_plain_kernel(const TX* __restrict__ x, int x_div, const TW* __restrict__ w, size_t expert_stride,
-                         const int* __restrict__ ids, TO* __restrict__ out, int P, int N, int K) {
+                         const int* __restrict__ ids, TO* __restrict__ out, int P, int N, int K, const float* __restrict__ act) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -108,7 +108,10 @@ expert_gemm_plain_kernel(const TX* __restrict__ x, int x_div, const TW* __restri
         if (EPI == BL_EPI_SWIGLU) u = fmaf(xv, bl_load(wr + (size_t)N * K + k), u);
     }
     a = bl_warp_sum(a);
-    if (EPI == BL_EPI_SWIGLU) a = bl_silu(a) * bl_warp_sum(u);
+    if (EPI == BL_EPI_SWIGLU) {
+        const BlGluArgs glu = bl_glu_args(act);
+        a = bl_glu(glu.kind, a, bl_warp_sum(u), glu.limit);
+    }
     if (lane == 0) bl_store(out + (size_t)p * N + n, a);
 }
 
@@ -186,14 +189,14 @@ __global__ void moe_combine_rows_kernel(const float* __restrict__ y, const int* 
 
 template <typename TX, typename TW, typename TO>
 int launch_expert(const void* x, int x_div, const void* w, size_t stride, const int* ids, void* out, int P, int N, int K, int epi,
-                  cudaStream_t s) {
+                  const float* act, cudaStream_t s) {
     const dim3 grid((N + WARPS - 1) / WARPS, P);
     if (epi == BL_EPI_NONE)
         BL_CUDA(bl_launch_dependent(expert_gemm_plain_kernel<TX, TW, TO, BL_EPI_NONE>, grid, dim3(WARPS * 32), 0, s, (const TX*)x, x_div,
-                                    (const TW*)w, stride, ids, (TO*)out, P, N, K));
+                                    (const TW*)w, stride, ids, (TO*)out, P, N, K, act));
     else if (epi == BL_EPI_SWIGLU)
         BL_CUDA(bl_launch_dependent(expert_gemm_plain_kernel<TX, TW, TO, BL_EPI_SWIGLU>, grid, dim3(WARPS * 32), 0, s, (const TX*)x, x_div,
-                                    (const TW*)w, stride, ids, (TO*)out, P, N, K));
+                                    (const TW*)w, stride, ids, (TO*)out, P, N, K, act));
     else
         BL_FAIL("bl_expert_gemm_plain: epilogue %d is not built", epi);
     BL_CHECK_LAUNCH("bl_expert_gemm_plain");
@@ -216,7 +219,8 @@ extern "C" int bl_moe_route(const float* z, int ldz, const void* correction, int
 }
 
 extern "C" int bl_expert_gemm_plain(const void* x, int x_dtype, int x_div, const void* w, int w_dtype, long long expert_stride,
-                                    const int* ids, void* out, int out_dtype, int P, int N, int K, int epilogue, void* stream) {
+                                    const int* ids, void* out, int out_dtype, int P, int N, int K, int epilogue, const float* act,
+                                    void* stream) {
     if (P <= 0) return 0;
     if (N <= 0 || K <= 0 || x_div <= 0 || P > 65535 * 32) BL_FAIL("bl_expert_gemm_plain: bad sizes P=%d N=%d K=%d", P, N, K);
     if (P > 65535) {                                          // the grid's y: in slices
@@ -225,18 +229,18 @@ extern "C" int bl_expert_gemm_plain(const void* x, int x_dtype, int x_div, const
         for (int p0 = 0; p0 < P; p0 += step) {
             const int n = P - p0 < step ? P - p0 : step;
             if (bl_expert_gemm_plain((const char*)x + (size_t)(p0 / x_div) * K * xe, x_dtype, x_div, w, w_dtype, expert_stride, ids + p0,
-                                     (char*)out + (size_t)p0 * N * oe, out_dtype, n, N, K, epilogue, stream)) return 1;
+                                     (char*)out + (size_t)p0 * N * oe, out_dtype, n, N, K, epilogue, act, stream)) return 1;
         }
         return 0;
     }
     cudaStream_t s = (cudaStream_t)stream;
     const size_t st = (size_t)expert_stride;
     if (x_dtype == BL_F32 && w_dtype == BL_F32 && out_dtype == BL_F32)
-        return launch_expert<float, float, float>(x, x_div, w, st, ids, out, P, N, K, epilogue, s);
+        return launch_expert<float, float, float>(x, x_div, w, st, ids, out, P, N, K, epilogue, act, s);
     if (x_dtype == BL_BF16 && w_dtype == BL_BF16 && out_dtype == BL_F32)
-        return launch_expert<__nv_bfloat16, __nv_bfloat16, float>(x, x_div, w, st, ids, out, P, N, K, epilogue, s);
+        return launch_expert<__nv_bfloat16, __nv_bfloat16, float>(x, x_div, w, st, ids, out, P, N, K, epilogue, act, s);
     if (x_dtype == BL_BF16 && w_dtype == BL_BF16 && out_dtype == BL_BF16)
-        return launch_expert<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, x_div, w, st, ids, out, P, N, K, epilogue, s);
+        return launch_expert<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, x_div, w, st, ids, out, P, N, K, epilogue, act, s);
     BL_FAIL("bl_expert_gemm_plain: unsupported dtypes x=%d w=%d out=%d", x_dtype, w_dtype, out_dtype);
 }
 

@@ -155,6 +155,24 @@ def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> None:
     _call(_lib().bl_add_row_vector, _p(x), _p(v), _dt(v), rows, d, _stream())
 
 
+def glu_args(kind: int, limit: float, device) -> Optional[torch.Tensor]:
+    """What a product with the gated epilogue (EPI_SWIGLU) takes in the place of a bias to compute another gated activation
+    than SiLU: the two 32-bit numbers {kind, limit} on the device (GLU_GELU_TANH, GLU_CLAMPED with its limit). None for SiLU."""
+    if kind == GLU_SILU:
+        return None
+    if kind not in (GLU_GELU_TANH, GLU_CLAMPED):
+        raise KernelError(f"glu_args: unknown gated activation {kind}")
+    return torch.tensor([float(kind), float(limit)], dtype=torch.float32, device=device)
+
+
+def _need_bias(bias: torch.Tensor, N: int, epilogue: int) -> None:
+    """A bias of N values; with the gated epilogue, which adds none, the two numbers of `glu_args`."""
+    if epilogue == EPI_SWIGLU:
+        _need(bias, "activation", torch.float32, (2,))
+    else:
+        _need(bias, "bias", None, (N,))
+
+
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                epilogue: int = EPI_NONE) -> None:
     """out = epilogue(x @ w.T) on CUDA cores with 32-bit accumulation. x may be a range of columns of a wider
@@ -166,7 +184,7 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Option
         raise KernelError("x: must be a CUDA matrix whose rows are contiguous")
     _need(w, "w", None, (rows_w, K)); _need(out, "out", None, (M, N))
     if bias is not None:
-        _need(bias, "bias", None, (N,))
+        _need_bias(bias, N, epilogue)
     _call(_lib().bl_gemm_plain_ld, _p(x), _dt(x), x.stride(0), _p(w), _dt(w), _p(bias), _dt(bias) if bias is not None else 0,
           _p(out), _dt(out), M, N, K, epilogue, _stream())
 
@@ -306,7 +324,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     rows_w = 2 * N if epilogue == EPI_SWIGLU else N
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (rows_w, K)); _need(out, "out", None, (M, N))
     if bias is not None:
-        _need(bias, "bias", None, (N,))
+        _need_bias(bias, N, epilogue)
     _call(_lib().bl_gemm_skinny, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
           M, N, K, epilogue, _stream())
 
@@ -528,7 +546,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
     rows_w = 2 * N if epilogue == EPI_SWIGLU else N
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (rows_w, K)); _need(out, "out", None, (M, N))
     if bias is not None:
-        _need(bias, "bias", None, (N,))
+        _need_bias(bias, N, epilogue)
     _call(_lib().bl_gemm_tc, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
           M, N, K, epilogue, _stream())
 
@@ -541,7 +559,7 @@ def gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
     rows_w = 2 * N if epilogue == EPI_SWIGLU else N
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (rows_w, K)); _need(out, "out", None, (M, N))
     if bias is not None:
-        _need(bias, "bias", None, (N,))
+        _need_bias(bias, N, epilogue)
     _call(_lib().bl_gemm_tc_pair, _p(x), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
           M, N, K, epilogue, _stream())
 
@@ -691,7 +709,7 @@ def gemm_skinny_scaled(hw: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ss:
     if ss.shape[0] != M:
         raise KernelError("gemm_skinny_scaled: ss and hw differ in rows")
     if bias is not None:
-        _need(bias, "bias", None, (N,))
+        _need_bias(bias, N, epilogue)
     _call(_lib().bl_gemm_skinny_scaled, _p(hw), _p(w), _p(bias), _dt(bias) if bias is not None else 0, _p(out), _dt(out),
           M, N, K, epilogue, _p(ss), ss.shape[1], ctypes.c_float(eps), _stream())
 
@@ -1251,9 +1269,15 @@ def moe_route(z: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_g
     _call(_lib().bl_moe_route, _p(z), ld, _p(correction), _vec_dt(correction), T, E, top, n_groups, keep, _p(ids), _p(wts), _stream())
 
 
-def expert_gemm_plain(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE) -> None:
+def expert_gemm_plain(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
+                      act: Optional[torch.Tensor] = None) -> None:
     """out[p] = epilogue(x[p // x_div] @ w[ids[p]].T): rows that each use the matrix of their own expert. w [E, N, K]
-    ([E, 2N, K], gate rows then up rows, for EPI_SWIGLU)."""
+    ([E, 2N, K], gate rows then up rows, for EPI_SWIGLU). `act`: the gated activation of EPI_SWIGLU when it is not SiLU
+    (`glu_args`)."""
+    if act is not None:
+        if epilogue != EPI_SWIGLU:
+            raise KernelError("an activation goes with the gated epilogue only")
+        _need(act, "act", torch.float32, (2,))
     P, N = out.shape
     K = x.shape[1]
     _need(x, "x"); _need(w, "w", x.dtype); _need(out, "out"); _need(ids, "ids", torch.int32)
@@ -1261,7 +1285,7 @@ def expert_gemm_plain(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.T
     if w.dim() != 3 or w.shape[1] != rows_w or w.shape[2] != K or ids.numel() != P or x.shape[0] * x_div != P:
         raise KernelError(f"expert_gemm_plain: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, {ids.numel()} ids do not fit")
     _call(_lib().bl_expert_gemm_plain, _p(x), _dt(x), x_div, _p(w), _dt(w), ctypes.c_longlong(w.stride(0)), _p(ids), _p(out), _dt(out),
-          P, N, K, epilogue, _stream())
+          P, N, K, epilogue, _p(act), _stream())
 
 
 def moe_combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:
@@ -1301,15 +1325,21 @@ def gather_rows(x: torch.Tensor, row_src: torch.Tensor, div: int, out: torch.Ten
     _call(_lib().bl_gather_rows, _p(x), _p(row_src), div, _p(out), out.shape[0], x.shape[1], _stream())
 
 
-def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE) -> None:
+def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
+                 act: Optional[torch.Tensor] = None) -> None:
     """out = epilogue(x @ w[expert of the row's tile].T) on tcgen05: x [tiles * 128, K] bfloat16 in tiles of 128 rows, w
-    [E, N, K] ([E, 2N, K], gate rows then up rows, for EPI_SWIGLU), tile_expert [tiles] (negative: an empty tile)."""
+    [E, N, K] ([E, 2N, K], gate rows then up rows, for EPI_SWIGLU), tile_expert [tiles] (negative: an empty tile). `act`:
+    the gated activation of EPI_SWIGLU when it is not SiLU (`glu_args`)."""
+    if act is not None:
+        if epilogue != EPI_SWIGLU:
+            raise KernelError("an activation goes with the gated epilogue only")
+        _need(act, "act", torch.float32, (2,))
     M, K = x.shape
     N = out.shape[1]
     E = w.shape[0]
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16, (E, 2 * N if epilogue == EPI_SWIGLU else N, K))
     _need(out, "out", None, (M, N)); _need(tile_expert, "tile_expert", torch.int32, (M // GROUPED_TILE,))
-    _call(_lib().bl_gemm_tc_grouped, _p(x), _p(w), _p(out), _dt(out), M, N, K, epilogue, E, _p(tile_expert), _stream())
+    _call(_lib().bl_gemm_tc_grouped, _p(x), _p(w), _p(out), _dt(out), M, N, K, epilogue, E, _p(tile_expert), _p(act), _stream())
 
 
 def moe_combine_rows(y: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:

@@ -127,8 +127,9 @@ class GluMLP(FeedForward):
     * "gelu_tanh":  0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u;
     * "clamped":    g' = min(g, limit), u' = clamp(u, -limit, limit); g' sigmoid(1.702 g') (u' + 1).
 
-    Gate and up are one joined product over [Wg; Wu] with 32-bit sums; the activation is evaluated on them in 32-bit; the
-    down product adds into the residual stream."""
+    Gate and up are one joined product over [Wg; Wu] whose epilogue evaluates the activation on the 32-bit sums (the
+    epilogue of `SwiGLU`, told which activation by two numbers on the device); the down product adds into the residual
+    stream."""
     graph_safe = True
     KINDS = {"silu": ops.GLU_SILU, "gelu_tanh": ops.GLU_GELU_TANH, "clamped": ops.GLU_CLAMPED}
 
@@ -139,7 +140,7 @@ class GluMLP(FeedForward):
         if activation == "clamped" and not limit > 0:
             raise ValueError(f"GluMLP: the clamped activation needs a positive limit, got {limit}")
         self.dim, self.hidden, self.activation, self.limit = dim, hidden, activation, float(limit)
-        self.w_gate_up = self.w_down = None
+        self.w_gate_up = self.w_down = self.act_args = None
 
     def local_specs(self):
         return {"w_gate": TensorSpec((self.hidden, self.dim), MATRIX),
@@ -149,12 +150,11 @@ class GluMLP(FeedForward):
     def place(self, local, dtype, device):
         self.w_gate_up = to_device_matrix(torch.cat([local["w_gate"], local["w_up"]], dim=0), dtype, device)
         self.w_down = to_device_matrix(local["w_down"], dtype, device)
+        self.act_args = ops.glu_args(self.KINDS[self.activation], self.limit, device)
 
     def _run(self, ctx, h, out, epilogue):
-        sums = ctx.empty((h.shape[0], 2 * self.hidden), torch.float32)
-        linear(ctx, h, self.w_gate_up, sums, None, EPI_NONE)
         act = ctx.empty((h.shape[0], self.hidden))
-        ops.glu_act(sums, act, self.KINDS[self.activation], self.limit)
+        linear(ctx, h, self.w_gate_up, act, self.act_args, EPI_SWIGLU)
         linear(ctx, act, self.w_down, out, None, epilogue)
 
     def forward(self, ctx, h, residual):
@@ -198,8 +198,7 @@ class RoutedExperts(FeedForward):
     groups can be chosen. The result is the weighted sum of the chosen experts' outputs, added in the order of the choice.
     The experts' matrices are stacked ([E, 2 * hidden, dim] gate rows then up rows, [E, dim, hidden]); every (token,
     chosen expert) pair is a row of two products whose rows each use the matrix of their own expert. `activation` /
-    `limit`: the experts' gated activation, as in `GluMLP` ("silu" is the products' own epilogue, the others a 32-bit pass
-    over the first product's sums)."""
+    `limit`: the experts' gated activation, as in `GluMLP`, evaluated in the first product's epilogue."""
     graph_safe = True
 
     def __init__(self, dim: int, hidden: int, n_experts: int, top: int, names: Dict[str, str], n_groups: int = 1,
@@ -216,7 +215,7 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"RoutedExperts: {top} experts a token out of {keep_groups} groups of {n_experts // n_groups}")
         self.dim, self.hidden, self.E, self.top = dim, hidden, n_experts, top
         self.n_groups, self.keep_groups, self.has_correction = n_groups, keep_groups, bool(correction)
-        self.router = self.correction = self.w_gate_up = self.w_down = None
+        self.router = self.correction = self.w_gate_up = self.w_down = self.act_args = None
         self.record = None               # a list: every step appends a copy of the experts it chose [T, top] (tests; kernels launched singly)
 
     def choice_specs(self):
@@ -244,6 +243,7 @@ class RoutedExperts(FeedForward):
         self.w_gate_up = to_device_matrix(torch.stack([torch.cat([local[f"gate{e}"], local[f"up{e}"]], dim=0) for e in range(self.E)]),
                                           dtype, device)
         self.w_down = to_device_matrix(torch.stack([local[f"down{e}"] for e in range(self.E)]), dtype, device)
+        self.act_args = ops.glu_args(GluMLP.KINDS[self.activation], self.limit, device)
 
     def route(self, ctx, h):
         """(experts [T, top] int32, weights [T, top] 32-bit) of the rows h."""
@@ -266,23 +266,13 @@ class RoutedExperts(FeedForward):
             rows = ctx.empty((row_src.numel(), self.dim))
             ops.gather_rows(h, row_src, self.top, rows)
             act = ctx.empty((row_src.numel(), self.hidden))
-            if self.activation == "silu":
-                ops.gemm_grouped(rows, self.w_gate_up, tile_expert, act, EPI_SWIGLU)
-            else:
-                sums = ctx.empty((row_src.numel(), 2 * self.hidden), torch.float32)
-                ops.gemm_grouped(rows, self.w_gate_up, tile_expert, sums, EPI_NONE)
-                ops.glu_act(sums, act, GluMLP.KINDS[self.activation], self.limit)
+            ops.gemm_grouped(rows, self.w_gate_up, tile_expert, act, EPI_SWIGLU, self.act_args)
             y = ctx.empty((row_src.numel(), self.dim), torch.float32)
             ops.gemm_grouped(act, self.w_down, tile_expert, y, EPI_NONE)
             ops.moe_combine_rows(y, pos, wts, out, add=add)
             return
         act = ctx.empty((T * self.top, self.hidden))
-        if self.activation == "silu":
-            ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, act, EPI_SWIGLU)
-        else:
-            sums = ctx.empty((T * self.top, 2 * self.hidden), torch.float32)
-            ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, sums, EPI_NONE)
-            ops.glu_act(sums, act, GluMLP.KINDS[self.activation], self.limit)
+        ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, act, EPI_SWIGLU, self.act_args)
         y = ctx.empty((T * self.top, self.dim), torch.float32)
         ops.expert_gemm_plain(act, 1, self.w_down, ids, y, EPI_NONE)
         ops.moe_combine(y, wts, out, add=add)

@@ -417,6 +417,55 @@ def test_gated_activations_and_the_table_of_experts():
     assert (out.double().cpu() - emb[tokens.cpu().long()].float().double() * 2.5).abs().max() <= 1e-5
 
 
+def gated(kind, g, u, limit):
+    from boring_llm_b200.kernels import ops
+    if kind == ops.GLU_GELU_TANH:
+        return pm.gelu_tanh(g) * u
+    if kind == ops.GLU_CLAMPED:
+        gc = torch.clamp(g, max=limit)
+        return gc * torch.sigmoid(1.702 * gc) * (torch.clamp(u, -limit, limit) + 1.0)
+    return g * torch.sigmoid(g) * u
+
+
+def test_gated_activations_in_the_epilogue_of_every_product():
+    """The joined gate/up product with the activation in its epilogue, on every kernel the row count can send it to (few
+    rows: W through registers; tcgen05 tiles on one SM; on pairs of SMs; CUDA cores in 32-bit), the grouped product and the
+    plain product over rows with a matrix each: against float64 on the same bfloat16 roundings."""
+    from boring_llm_b200.kernels import ops
+    K, N, limit = 256, 192, 0.7
+    seen = set()
+    for kind in (ops.GLU_SILU, ops.GLU_GELU_TANH, ops.GLU_CLAMPED):
+        args = ops.glu_args(kind, limit, DEV)
+        assert (args is None) == (kind == ops.GLU_SILU)
+        for M in (3, 16, 40, 130, 600):
+            x = rnd(M, K, seed=M, scale=0.5).bfloat16().double()
+            w = rnd(2 * N, K, seed=M + 1, scale=0.2).bfloat16().double()
+            want = gated(kind, x @ w[:N].T, x @ w[N:].T, limit)
+            for dtype, tol in ((torch.bfloat16, 2e-2), (torch.float32, 1e-5)):
+                out = torch.empty((M, N), dtype=dtype, device=DEV)
+                seen.add(ops.gemm_kernel(dev(x, dtype), dev(w, dtype), N, args, ops.EPI_SWIGLU))
+                ops.gemm(dev(x, dtype), dev(w, dtype), out, args, ops.EPI_SWIGLU)
+                assert (out.double().cpu() - want).abs().max() <= tol * max(1.0, want.abs().max().item()), (kind, M, dtype)
+        # three matrices; rows with a matrix each (plain), and the same rows in tiles of 128 behind the plan (grouped)
+        E, T, top = 3, 50, 2
+        x = rnd(T, K, seed=9, scale=0.5).bfloat16().double()
+        w = rnd(E, 2 * N, K, seed=10, scale=0.2).bfloat16().double()
+        ids = torch.stack([torch.randperm(E, generator=torch.Generator().manual_seed(t))[:top] for t in range(T)]).int()
+        want = torch.stack([gated(kind, x[t] @ w[e, :N].T, x[t] @ w[e, N:].T, limit) for t in range(T) for e in ids[t].tolist()])
+        for dtype, tol in ((torch.bfloat16, 2e-2), (torch.float32, 1e-5)):
+            out = torch.empty((T * top, N), dtype=dtype, device=DEV)
+            ops.expert_gemm_plain(dev(x, dtype), top, dev(w, dtype), ids.to(DEV), out, ops.EPI_SWIGLU, args)
+            assert (out.double().cpu() - want).abs().max() <= tol * max(1.0, want.abs().max().item()), (kind, "rows", dtype)
+        pos, row_src, tile_expert = ops.moe_plan(ids.to(DEV), E)
+        rows = torch.zeros((row_src.numel(), K), dtype=torch.bfloat16, device=DEV)
+        ops.gather_rows(dev(x, torch.bfloat16), row_src, top, rows)
+        out = torch.empty((row_src.numel(), N), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_grouped(rows, dev(w, torch.bfloat16), tile_expert, out, ops.EPI_SWIGLU, args)
+        got = out[pos.long()].double().cpu()
+        assert (got - want).abs().max() <= 2e-2 * max(1.0, want.abs().max().item()), (kind, "grouped")
+    assert {"plain", "skinny", "tc", "pair"} <= seen, seen
+
+
 def test_the_command_line_and_the_trace_program_on_a_model_folder(folders, tmp_path):
     """`bin/boring-llm` generates what the plain implementation's arg-max gives, and `bin/trace_run`, started as a user
     would start it, writes the logits of a mixed trace (float32, and bfloat16 on poisoned pools)."""
