@@ -399,7 +399,8 @@ int bl_glu_act(const float* x, long long ld_x, void* y, int y_dtype, long long l
 // rotated in pairs (j, j + rot_half) by float(position) * inv_freq[j], cos and sin times mscale] (cache null: skipped);
 // cache [pages, page_size, rank + rot_dim]. bl_head_gemm_plain: out[t, h, n] = sum_k x[t, h, k] W[h][n, k] (* sigmoid(gate[t, h * N + n])),
 // every operand by its strides in elements. bl_rope_heads: out[t, h, out_off + .] = q[t, h, off + .] (n values, the
-// first 2 * rot_half rotated).
+// first 2 * rot_half rotated); with n_lead > 0 also lead_out[t, h, .] = lead[t, h, .] (n_lead values of every head, `lead` strided as q,
+// lead_out of out's dtype with strides of its own).
 // bl_latent_attention_plain: q [T, H, dk], out [T, H, dv]: softmax over the visible cached rows (window 0: all) of
 // q . row * scale with an optional sink per head in the denominator, applied to the rows' first dv values.
 int bl_latent_prep(const float* proj, int ld, int off_q, int q_rank, int off_kv, int rank, int rot_dim, int rot_half, const void* q_norm_w,
@@ -411,7 +412,7 @@ int bl_head_gemm_plain(const void* x, int x_dtype, long long ldx, long long x_he
                        int N, int K, const float* gate, long long ld_gate, void* stream);
 int bl_rope_heads(const float* q, long long ld, long long head_stride, int off, const int* positions, const float* inv_freq,
                   int n, int rot_half, float mscale, void* out, int out_dtype, long long ld_out, long long out_head, int out_off, int T,
-                  int H, void* stream);
+                  int H, const float* lead, int n_lead, void* lead_out, long long ld_lead, long long lead_head, void* stream);
 int bl_latent_attention_plain(const void* q, const void* cache, int dtype, const int* tok_req, const int* cu_q, const int* ctx_len,
                               const int* block_table, int max_pages, void* out, int T, int H, int dk, int dv, int page_size,
                               int window, float scale, const void* sinks, int sink_dtype, void* stream);

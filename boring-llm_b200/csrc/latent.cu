@@ -96,7 +96,8 @@ template <typename TO>
 __global__ void __launch_bounds__(THREADS)
 rope_heads_kernel(const float* q, size_t ld, size_t head_stride, int off, const int* __restrict__ positions,
                   const float* __restrict__ inv_freq, int n, int rot_half, float mscale, TO* __restrict__ out, size_t ld_out,
-                  size_t out_head, int out_off, int H) {
+                  size_t out_head, int out_off, int H, const float* lead, int n_lead, TO* __restrict__ lead_out, size_t ld_lead,
+                  size_t lead_head) {
     bl_pdl_trigger();
     bl_pdl_wait();
     extern __shared__ float cs[];                      // cos [rot_half], sin [rot_half]
@@ -120,6 +121,11 @@ rope_heads_kernel(const float* q, size_t ld, size_t head_stride, int off, const 
     for (int e = threadIdx.x; e < H * rest; e += THREADS) {
         const int h = e / rest, d = 2 * rot_half + e % rest;
         bl_store(out + (size_t)t * ld_out + (size_t)h * out_head + out_off + d, q[(size_t)t * ld + (size_t)h * head_stride + off + d]);
+    }
+    // another slice of every head (the part of q that is not rotated), strided as q, cast into a tensor of its own
+    for (int e = threadIdx.x; e < H * n_lead; e += THREADS) {
+        const int h = e / n_lead, d = e % n_lead;
+        bl_store(lead_out + (size_t)t * ld_lead + (size_t)h * lead_head + d, lead[(size_t)t * ld + (size_t)h * head_stride + d]);
     }
 }
 
@@ -287,13 +293,16 @@ extern "C" int bl_head_gemm_plain(const void* x, int x_dtype, long long ldx, lon
 
 extern "C" int bl_rope_heads(const float* q, long long ld, long long head_stride, int off, const int* positions,
                              const float* inv_freq, int n, int rot_half, float mscale, void* out, int out_dtype, long long ld_out,
-                             long long out_head, int out_off, int T, int H, void* stream) {
+                             long long out_head, int out_off, int T, int H, const float* lead, int n_lead, void* lead_out,
+                             long long ld_lead, long long lead_head, void* stream) {
     if (T <= 0 || n <= 0) return 0;
+    if (n_lead < 0 || (n_lead > 0 && (lead == nullptr || lead_out == nullptr))) BL_FAIL("bl_rope_heads: a second slice of %d values without its tensors", n_lead);
     if (H <= 0 || off < 0 || out_off < 0 || rot_half < 0 || 2 * rot_half > n) BL_FAIL("bl_rope_heads: bad sizes H=%d n=%d pairs=%d offsets %d, %d", H, n, rot_half, off, out_off);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)(2 * rot_half + 1) * sizeof(float);
 #define BL_GO(TO) BL_CUDA(bl_launch_dependent(rope_heads_kernel<TO>, dim3(T), dim3(THREADS), smem, s, q, (size_t)ld, (size_t)head_stride, off, \
-        positions, inv_freq, n, rot_half, mscale, (TO*)out, (size_t)ld_out, (size_t)out_head, out_off, H))
+        positions, inv_freq, n, rot_half, mscale, (TO*)out, (size_t)ld_out, (size_t)out_head, out_off, H, lead, n_lead, (TO*)lead_out, \
+        (size_t)ld_lead, (size_t)lead_head))
     if (out_dtype == BL_F32) BL_GO(float);
     else if (out_dtype == BL_BF16) BL_GO(__nv_bfloat16);
     else BL_FAIL("bl_rope_heads: unknown dtype %d", out_dtype);

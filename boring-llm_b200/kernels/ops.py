@@ -1425,18 +1425,26 @@ def head_gemm_plain(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: O
 
 
 def rope_heads(q: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, rot_half: int, mscale: float,
-               out: torch.Tensor) -> None:
+               out: torch.Tensor, lead: Optional[torch.Tensor] = None, lead_out: Optional[torch.Tensor] = None) -> None:
     """out[t, h, :] = q[t, h, :] with its first 2 * rot_half values rotated in pairs (j, j + rot_half) by
     float(position[t]) * inv_freq[j], cos and sin times mscale. q: 32-bit view [T, H, n], out a view of the same shape, last
-    dimensions contiguous."""
+    dimensions contiguous. `lead` / `lead_out`: in the same launch, another slice of the same rows (a view [T, H, m] with q's
+    strides: the part of a head that is not rotated) cast into a tensor of its own, of out's dtype."""
     T, H, n = q.shape
     if n < 2 * rot_half or q.dtype != torch.float32:
         raise KernelError("rope_heads: q must be a 32-bit view [T, H, >= 2 * rot_half]")
     ldq, qh = _head_view(q, "q", T, H, n)
     ldo, oh = _head_view(out, "out", T, H, n)
     _need(positions, "positions", torch.int32, (T,)); _need(inv_freq, "inv_freq", torch.float32)
+    m, ldl, lh = 0, 0, 0
+    if lead is not None:
+        m = lead.shape[2]
+        if lead.dtype != torch.float32 or _head_view(lead, "lead", T, H, m) != (ldq, qh) or lead_out is None or lead_out.dtype != out.dtype:
+            raise KernelError("rope_heads: the second slice must be a 32-bit view with q's strides, its result of out's dtype")
+        ldl, lh = _head_view(lead_out, "lead_out", T, H, m)
     _call(_lib().bl_rope_heads, _p(q), ctypes.c_longlong(ldq), ctypes.c_longlong(qh), 0, _p(positions), _p(inv_freq), n, rot_half,
-          ctypes.c_float(mscale), _p(out), _dt(out), ctypes.c_longlong(ldo), ctypes.c_longlong(oh), 0, T, H, _stream())
+          ctypes.c_float(mscale), _p(out), _dt(out), ctypes.c_longlong(ldo), ctypes.c_longlong(oh), 0, T, H,
+          _p(lead), m, _p(lead_out), ctypes.c_longlong(ldl), ctypes.c_longlong(lh), _stream())
 
 
 def latent_attention_plain(q: torch.Tensor, cache: torch.Tensor, tok_req: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor,

@@ -138,12 +138,13 @@ class LatentAttention(Mixer):
         linear(ctx, cq, self.wuq, q, None, EPI_NONE)
         q3 = q.view(T, H, self.dn + self.dr)
         qn = ctx.empty((H, Tp, self.dn))
-        ops.rope_heads(q3[:, :, :self.dn], ctx.positions, self.rotary.inv_freq, 0, 1.0, qn.transpose(0, 1)[:T])     # a cast, head-major
         q_rot = None
-        if self.dr:
+        if self.dr:                                   # one launch: the rotated part rotated, the other part cast, both head-major
             q_rot = ctx.empty((H, Tp, self.dr))
             ops.rope_heads(q3[:, :, self.dn:], ctx.positions, self.rotary.inv_freq, self.rotary.rot_half, self.rotary.mscale,
-                           q_rot.transpose(0, 1)[:T])
+                           q_rot.transpose(0, 1)[:T], lead=q3[:, :, :self.dn], lead_out=qn.transpose(0, 1)[:T])
+        else:
+            ops.rope_heads(q3[:, :, :self.dn], ctx.positions, self.rotary.inv_freq, 0, 1.0, qn.transpose(0, 1)[:T])     # a cast
         q_lat = ctx.empty((H, Tp, self.rank))
         ops.gemm_grouped(qn.view(H * Tp, self.dn), self.wuk_t, tile_head, q_lat.view(H * Tp, self.rank), EPI_NONE)
         lat = ctx.empty((H, Tp, self.rank))
