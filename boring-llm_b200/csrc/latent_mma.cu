@@ -9,9 +9,11 @@
 // double-buffered through cp.async. Per key block:
 //   scores: warp (row group rg, quarter qt) multiplies its 16 rows by the 16 keys of its quarter over all of dk and
 //           leaves the raw 32-bit scores in shared memory;
-//   values: every warp reads its 16 rows' 64 scores back in fragment layout, runs the online softmax on them (the four
-//           warps of a row group compute the same statistics) and multiplies the weights by its own quarter of the value
-//           columns, up to NTW tiles of 8 columns.
+//   softmax: warp w owns rows 4w .. 4w + 3 (eight lanes a row): mask, running maximum and sum, and the weights, which
+//           it writes as bfloat16 into the place of the row's scores beside the factor for the row's sums so far (no
+//           exponential is computed twice);
+//   values: warp (rg, qt) scales its sums by the factors of its 16 rows, fetches the weights as the left operand and
+//           multiplies them by its own quarter of the value columns, up to NTW tiles of 8 columns.
 // Each phase has the tensor-core work split four ways without any product computed twice; the output of 16 rows x 512
 // value columns, which no warp could hold, is 64 registers a thread. A sink per head joins the denominator at the end.
 #include "common.cuh"
@@ -100,7 +102,8 @@ latent_attention_mma_kernel(const LatentParams p) {
     const int row = dkp + PAD;
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);           // [ROWS][row]
     __nv_bfloat16* ks = qs + ROWS * row;                                      // [2][KB][row]
-    float* ss = reinterpret_cast<float*>(ks + 2 * KB * row);                  // [ROWS][SROW]
+    float* ss = reinterpret_cast<float*>(ks + 2 * KB * row);                  // [ROWS][SROW]: scores, then the weights in their place
+    float* fac = ss + ROWS * SROW;                                            // [2][ROWS]: a row's factor for its sums so far; its last factor
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int rg = warp >> 2, qt = warp & 3;
     const int mi = lane >> 3, ri = lane & 7;                      // ldmatrix: which 8x8 matrix, which row of it
@@ -160,18 +163,16 @@ latent_attention_mma_kernel(const LatentParams p) {
     }
     if (b_begin < b_end) load_keys(ks, row, p, table, dk, b_begin * KB, lo, hi);
     cp_async_commit();
-    // rows g and g + 8 of this warp's row group
-    int pos[2], lo_row[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int rr = rg * 16 + g + 8 * h;
-        pos[h] = rr < n_rows ? (SINGLE ? p_first : p_first + rr) : -1;        // a row that is no query sees nothing
-        lo_row[h] = p.window > 0 ? max(0, pos[h] - p.window + 1) : 0;
-    }
+    // The softmax of a row belongs to ONE warp: warp w owns rows 4w .. 4w + 3, eight lanes a row, eight keys a lane. It keeps
+    // the row's maximum and sum, and leaves the weights (bfloat16, in the place of the row's scores) and the factor for the
+    // sums so far in shared memory, where the warps of the row's group fetch them as the left operand of the value product.
+    const int own = warp * 4 + (lane >> 3), sub = lane & 7;
+    const int pos = own < n_rows ? (SINGLE ? p_first : p_first + own) : -1;   // a row that is no query sees nothing
+    const int lo_row = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     float o[NTW][4];
 #pragma unroll
     for (int n = 0; n < NTW; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float m = -INFINITY, l = 0.f;
     const int v_cols = (p.rank + 15) & ~15;                       // value columns in pairs of tiles
     for (int b = b_begin; b < b_end; ++b) {
         __nv_bfloat16* stage = ks + ((b - b_begin) & 1) * KB * row;
@@ -183,6 +184,7 @@ latent_attention_mma_kernel(const LatentParams p) {
         }
         {   // scores of 16 rows x the 16 keys of this warp's quarter
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 2
             for (int kk = 0; kk < dkp / 16; ++kk) {
                 unsigned a[4], bf[4];
                 ldmatrix_x4(a, qs + (rg * 16 + (mi & 1) * 8 + ri) * row + kk * 16 + (mi >> 1) * 8);
@@ -198,61 +200,53 @@ latent_attention_mma_kernel(const LatentParams p) {
             }
         }
         __syncthreads();
-        float s[KB / 8][4];
-        float mx[2] = {-INFINITY, -INFINITY};
+        {   // the owner's pass over its row: mask, maximum, weights, sum
+            float* srow = ss + own * SROW + sub * 8;
+            const float4 u = *reinterpret_cast<const float4*>(srow), v = *reinterpret_cast<const float4*>(srow + 4);
+            float e[8] = {u.x, u.y, u.z, u.w, v.x, v.y, v.z, v.w};
+            float mx = -INFINITY;
 #pragma unroll
-        for (int n = 0; n < KB / 8; ++n) {
-            const float* s0 = ss + (rg * 16 + g) * SROW + n * 8 + 2 * t;
-            const float2 u = *reinterpret_cast<const float2*>(s0);
-            const float2 v = *reinterpret_cast<const float2*>(s0 + 8 * SROW);
-            s[n][0] = u.x; s[n][1] = u.y; s[n][2] = v.x; s[n][3] = v.y;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int j = b * KB + n * 8 + 2 * t + (c & 1);
-                const bool seen = j <= pos[c >> 1] && j >= lo_row[c >> 1];
-                s[n][c] = seen ? s[n][c] : -INFINITY;
-                mx[c >> 1] = fmaxf(mx[c >> 1], s[n][c]);
+            for (int c = 0; c < 8; ++c) {
+                const int j = b * KB + sub * 8 + c;
+                e[c] = (j <= pos && j >= lo_row) ? e[c] : -INFINITY;
+                mx = fmaxf(mx, e[c]);
             }
-        }
-        float m_use[2];
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            const float m_new = fmaxf(m, mx * p.scale_log2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;             // a row that has seen no key yet
+            const float alpha = ex2(m - m_use);                               // 2^-inf = 0 on the first block
+            m = m_new;
+            float part = 0.f;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-            const float m_new = fmaxf(m[h], mx[h] * p.scale_log2);
-            m_use[h] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen no key yet
-            if (m_new != m[h]) {
-                const float alpha = ex2(m[h] - m_use[h]);         // 2^-inf = 0 on the first block
-                m[h] = m_new;
-                l[h] *= alpha;
-#pragma unroll
-                for (int n = 0; n < NTW; ++n) { o[n][2 * h] *= alpha; o[n][2 * h + 1] *= alpha; }
+            for (int c = 0; c < 8; ++c) {
+                e[c] = ex2(fmaf(e[c], p.scale_log2, -m_use));                 // a masked score is -inf: 2^-inf = 0
+                part += e[c];
             }
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            part += __shfl_xor_sync(0xffffffffu, part, 4);
+            l = l * alpha + part;
+            __syncwarp();                                                     // the row's scores have been read: its weights take their place
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(ss + own * SROW) + sub * 8) =
+                make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+            if (sub == 0) fac[own] = alpha;
         }
-        float part[2] = {0.f, 0.f};
+        __syncthreads();
+        {
+            const float a0 = fac[rg * 16 + g], a1 = fac[rg * 16 + g + 8];
+            if (a0 != 1.f || a1 != 1.f) {
 #pragma unroll
-        for (int n = 0; n < KB / 8; ++n) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float e = ex2(fmaf(s[n][c], p.scale_log2, -m_use[c >> 1]));     // a masked score is -inf: 2^-inf = 0
-                s[n][c] = e;
-                part[c >> 1] += e;
+                for (int n = 0; n < NTW; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
             }
-        }
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            part[h] += __shfl_xor_sync(0xffffffffu, part[h], 1);
-            part[h] += __shfl_xor_sync(0xffffffffu, part[h], 2);
-            l[h] += part[h];
         }
         // out += P . V over this warp's value columns, P rounded to bfloat16 as the tensor cores' left operand
+        const __nv_bfloat16* ps = reinterpret_cast<const __nv_bfloat16*>(ss);
 #pragma unroll
         for (int kk = 0; kk < KB / 16; ++kk) {
             unsigned a[4];
-            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            ldmatrix_x4(a, ps + (rg * 16 + (mi & 1) * 8 + ri) * (2 * SROW) + kk * 16 + (mi >> 1) * 8);
 #pragma unroll
             for (int np = 0; np < NTW / 2; ++np) {
                 const int col = (qt * NTW + 2 * np) * 8;
@@ -278,23 +272,31 @@ latent_attention_mma_kernel(const LatentParams p) {
                 const int col = (qt * NTW + n) * 8 + 2 * t;
                 if (col < p.rank) *reinterpret_cast<float2*>(po + col) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
             }
-            if (qt == 0 && t == 0) { p.part_ml[2 * prow] = m[h]; p.part_ml[2 * prow + 1] = l[h]; }
+        }
+        if (sub == 0 && own < n_rows) {
+            const size_t prow = ((size_t)item * p.H + head0 + own) * p.n_splits + split;
+            p.part_ml[2 * prow] = m;
+            p.part_ml[2 * prow + 1] = l;
         }
         return;
     }
+    if (sub == 0 && own < n_rows) {
+        float f = 1.f, den = l;
+        if (p.sinks) {                                            // one more term of the denominator: unscaled, no value
+            const float sk = bl_load_any(p.sinks, p.sink_dtype, SINGLE ? head0 + own : head0) * 1.4426950408889634f;
+            const float mm = fmaxf(m, sk);
+            f = exp2f(m - mm);
+            den = den * f + exp2f(sk - mm);
+        }
+        fac[ROWS + own] = den > 0.f ? f / den : 0.f;
+    }
+    __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int rr = rg * 16 + g + 8 * h;
         if (rr >= n_rows) continue;
         const int head = SINGLE ? head0 + rr : head0;
-        float f = 1.f, den = l[h];
-        if (p.sinks) {                                            // one more term of the denominator: unscaled, no value
-            const float sk = bl_load_any(p.sinks, p.sink_dtype, head) * 1.4426950408889634f;
-            const float mm = fmaxf(m[h], sk);
-            f = exp2f(m[h] - mm);
-            den = den * f + exp2f(sk - mm);
-        }
-        const float inv = den > 0.f ? f / den : 0.f;
+        const float inv = fac[ROWS + rr];
         const size_t at = (size_t)head * p.Tp + (size_t)(q_begin + (SINGLE ? tok0 : tok0 + rr));
         __nv_bfloat16* dst = p.out + at * p.rank;
 #pragma unroll
@@ -338,7 +340,7 @@ latent_merge_kernel(const LatentParams p) {
 
 size_t smem_bytes(int dk) {
     const int row = ((dk + 15) & ~15) + PAD;
-    return (size_t)(ROWS + 2 * KB) * row * sizeof(__nv_bfloat16) + (size_t)ROWS * SROW * sizeof(float);
+    return (size_t)(ROWS + 2 * KB) * row * sizeof(__nv_bfloat16) + (size_t)ROWS * (SROW + 2) * sizeof(float);
 }
 
 template <int NTW, bool SINGLE>
