@@ -315,7 +315,7 @@ def attention_oracle(ctx, q_lens, rows, q, rank, window, scale, sinks):
     return torch.cat(out)
 
 
-@pytest.mark.parametrize("H,rank,rot,window", [(4, 32, 8, 20), (3, 96, 16, 64), (35, 160, 32, 0), (2, 272, 8, 17), (16, 512, 64, 130)])
+@pytest.mark.parametrize("H,rank,rot,window", [(4, 32, 8, 20), (3, 96, 16, 64), (35, 160, 32, 0), (2, 272, 8, 17), (16, 512, 64, 130), (3, 520, 24, 75)])
 def test_latent_attention_kernels(H, rank, rot, window):
     from boring_llm_b200.kernels import ops
     from boring_llm_b200.parts.attention import attention_plan
