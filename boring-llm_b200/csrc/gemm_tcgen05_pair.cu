@@ -380,10 +380,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     uint32_t u[32];
                     tmem_ld32(lane_addr + BN / 2 + c * 32, u);
                     tmem_ld_wait();
+                    if (glu.kind == BL_GLU_SILU) {                              // one branch a chunk, the loops as they were
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float g1 = __uint_as_float(r[j]) * row_scale, u1 = __uint_as_float(u[j]) * row_scale;
-                        r[j] = __float_as_uint(bl_glu_fast(glu.kind, g1, u1, glu.limit));
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(bl_silu_fast(__uint_as_float(r[j]) * row_scale) * (__uint_as_float(u[j]) * row_scale));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            r[j] = __float_as_uint(bl_glu_fast(glu.kind, __uint_as_float(r[j]) * row_scale, __uint_as_float(u[j]) * row_scale, glu.limit));
                     }
                 } else {
                     tmem_ld_wait();
