@@ -152,6 +152,15 @@ class GluMLP(FeedForward):
         self.w_down = to_device_matrix(local["w_down"], dtype, device)
         self.act_args = ops.glu_args(self.KINDS[self.activation], self.limit, device)
 
+    def takes_pending_norm_at(self, rows: int) -> bool:
+        """gate/up finishes a norm that the product before has begun on the register-streaming kernel (a decode step's 2
+        to 16 rows), and, with SiLU, on pairs of SMs (many rows), as `SwiGLU` does."""
+        if rows >= ops.PAIR_MIN_ROWS:
+            return self.act_args is None and self.w_gate_up is not None and self.w_gate_up.dtype == torch.bfloat16
+        return (ops.SKINNY_LINK_MIN_ROWS <= rows <= ops.SKINNY_LINK_MAX_ROWS and self.w_gate_up is not None
+                and self.w_gate_up.dtype == torch.bfloat16 and -(-self.hidden // 16) <= ops.SKINNY_LINK_MAX_BLOCKS
+                and not ops.gemm_streams_better(self.w_gate_up))
+
     def _run(self, ctx, h, out, epilogue):
         act = ctx.empty((h.shape[0], self.hidden))
         linear(ctx, h, self.w_gate_up, act, self.act_args, EPI_SWIGLU)
@@ -180,8 +189,12 @@ class SumFeedForward(FeedForward):
         return all(getattr(p, "graph_safe", False) for p in self.parts)
 
     def forward(self, ctx, h, residual):
-        for p in self.parts:
+        # only the LAST part's addition may begin the norm that reads the stream next: the others' sums are not the row yet
+        after = ctx.next_norm
+        for i, p in enumerate(self.parts):
+            ctx.next_norm = after if i == len(self.parts) - 1 else None
             p.forward(ctx, h, residual)
+        ctx.next_norm = after
 
     def apply(self, ctx, h, out):
         self.parts[0].apply(ctx, h, out)

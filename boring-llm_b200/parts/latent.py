@@ -102,6 +102,13 @@ class LatentAttention(Mixer):
     def cache_spec(self):
         return PagedKVSpec(1, self.rank + self.dr, self.cache_window, self.rank, values_in_keys=True)
 
+    def takes_pending_norm_at(self, rows: int) -> bool:
+        """The joined first product finishes an RMS norm that the product before has begun where it runs on the
+        register-streaming kernel (a decode step's 2 to 16 rows); elsewhere the product before need not begin one."""
+        return (ops.SKINNY_LINK_MIN_ROWS <= rows <= ops.SKINNY_LINK_MAX_ROWS and self.w_in is not None
+                and self.w_in.dtype == torch.bfloat16 and -(-self.n_in // 16) <= ops.SKINNY_LINK_MAX_BLOCKS
+                and not ops.gemm_streams_better(self.w_in))
+
     def plan_step(self, q_lens, ctx_lens, filler=None):
         return PLAN_KEY, attention_plan(q_lens, ctx_lens, filler)
 
