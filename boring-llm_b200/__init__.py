@@ -2,8 +2,8 @@
 typed configuration and registry, safetensors weights, layers built from parts, a paged cache
 manager, one step function over mixed batches, a scheduler, sampling, and hand-written CUDA kernels.
 """
-from .config import (ConfigError, EngineOptions, FezopelConfig, KavotarConfig, MiforaxConfig, Qwen2Config, load_config, register_architecture,
-                     registered_architectures)
+from .config import (ConfigError, DapuzenConfig, EngineOptions, FezopelConfig, KavotarConfig, MiforaxConfig, Qwen2Config, load_config,
+                     register_architecture, registered_architectures)
 from .weights import WeightsError
 from .models import build_model, load_model, load_random_model, write_random_model
 

@@ -216,6 +216,11 @@ int bl_attention_plain_ext(const void* q, const void* k_cache, const void* v_cac
                            const int* tok_req, const int* cu_q, const int* ctx_len, const int* block_table,
                            int max_pages, void* out, int T, int H, int KV, int dh, int dv, int page_size, int window,
                            float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate, void* stream);
+// ... and a cap c > 0 on the scores: s <- c tanh(s / c) on the scaled score, before the softmax (0: none).
+int bl_attention_plain_cap(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                           const int* tok_req, const int* cu_q, const int* ctx_len, const int* block_table,
+                           int max_pages, void* out, int T, int H, int KV, int dh, int dv, int page_size, int window,
+                           float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate, float softcap, void* stream);
 
 // y[r, :] = (x[src, :] - mean) / sqrt(var + eps) * w + b (b may be null), src = row_idx ? row_idx[r] : r; var is the
 // mean of the squared deviations; statistics in 32-bit.
@@ -288,6 +293,23 @@ int bl_head_norm_gate(const float* o, const void* w, int w_dtype, const float* g
 int bl_conv_silu_unit(const float* x, int ld, const float* taps, int n_taps, const float* tail, long long slot_stride,
                       const int* slots, const int* tok_req, const int* cu_q, float* y, int T, int C, int unit_heads,
                       int scaled_heads, int dk, float q_scale, float unit_eps, void* stream);
+// bl_conv_silu_unit with a bias per channel (null: none) that each channel's sum starts from.
+int bl_conv_silu_unit_bias(const float* x, int ld, const float* taps, int n_taps, const float* tail, long long slot_stride,
+                           const int* slots, const int* tok_req, const int* cu_q, float* y, int T, int C, int unit_heads,
+                           int scaled_heads, int dk, float q_scale, float unit_eps, const void* bias, int bias_dtype, void* stream);
+// In front of a recurrence with a fixed decay per head: q (columns 0 ..) and k (from off_k) of proj rotated by position
+// (pairs (i, i + rot_half) of each head's first 2 * rot_half values), k times k_scale, decay_out[t, h, :] = head_decay[h].
+int bl_rope_decay_prep(const float* proj, int ld, int off_k, const int* positions, const float* inv_freq, int rot_half,
+                       const float* head_decay, float k_scale, float* q_out, float* k_out, float* decay_out, int T, int H, int dk,
+                       void* stream);
+// In front of a selective state-space recurrence: dt = softplus(raw[t, h] + dt_bias[h]); decay_out[t, h, :n_state] =
+// exp(-rate[h] * dt); v_out[t, h, :] = dt * x[t, h, :].
+int bl_ssd_prep(const float* raw, int ld_raw, const void* dt_bias, int bias_dtype, const float* rate, const float* x, int ld_x,
+                float* decay_out, float* v_out, int T, int H, int n_state, int dv, void* stream);
+// y = rms_norm_in_parts((o + skip[c / dv] * x) * silu(z)) * w: the gate in front of the norm, n_parts equal parts of a row of
+// `width` values each normed by its own root mean square. x / skip, z and w may be null.
+int bl_gated_group_norm(const float* o, const float* x, int ld_x, const void* skip, int skip_dtype, int dv, const float* z, int ld_z,
+                        const void* w, int w_dtype, void* y, int y_dtype, int T, int width, int n_parts, float eps, void* stream);
 // The tail of every request with tokens becomes its last n_taps - 1 inputs (after bl_conv_silu_unit has read it).
 int bl_conv_tail_update(const float* x, int ld, int n_taps, float* tail, long long slot_stride, const int* slots,
                         const int* cu_q, int R, int C, void* stream);
@@ -340,6 +362,12 @@ int bl_cast_rows(const float* x, void* y, int y_dtype, long long count, void* st
 int bl_pair_rms_mean(const float* a, const void* wa, int wa_dtype, const float* b, const void* wb, int wb_dtype, float rms_eps,
                      float* out, int rows, int d, void* stream);
 int bl_softcap(float* x, long long count, float cap, void* stream);
+// x += ca * a + cb * b (32-bit, `count` values); x[r, :] += sigmoid(gate[r * ld_gate]) * a[r, :] (one gate logit per row).
+int bl_add_scaled_pair(float* x, const float* a, float ca, const float* b, float cb, long long count, void* stream);
+int bl_add_row_gated(float* x, const float* a, const float* gate, long long ld_gate, int rows, int d, void* stream);
+// y = xIELU(x) on 32-bit sums, args = {softplus(p), 1/2 + softplus(q)} on the device: v > 0: args[0] v^2 + v / 2, else
+// args[1] (e^v - 1 - v) + v / 2.
+int bl_xielu(const float* x, long long ld_x, void* y, int y_dtype, long long ld_y, int rows, int cols, const float* args, void* stream);
 
 // Attention over the query's own chunk of positions with the heads' softmax weights mixed afterwards (attention_talk.cu).
 // Position i sees j in [i - i % chunk, i] (chunk 0: from 0; window > 0 also j > i - window); score = q . k * scale *
@@ -372,6 +400,20 @@ int bl_moe_route(const float* z, int ldz, const void* correction, int corr_dtype
 int bl_expert_gemm_plain(const void* x, int x_dtype, int x_div, const void* w, int w_dtype, long long expert_stride, const int* ids,
                          void* out, int out_dtype, int P, int N, int K, int epilogue, const float* act, void* stream);
 int bl_moe_combine(const float* y, const float* wts, float* out, int T, int top, int d, int add, void* stream);
+// The same with further choices. bl_moe_route_ext: score_kind BL_SCORE_SIGMOID, or BL_SCORE_SOFTMAX (softmax of z over all E);
+// group_top 2: a group's score is the sum of its two largest choice scores, 1: its largest. Identity experts are the expert
+// numbers from n_real on: no matrix, no row in a product; the weighted sums take the token's input row x[t, :] for them.
+#define BL_SCORE_SIGMOID 0
+#define BL_SCORE_SOFTMAX 1
+int bl_moe_route_ext(const float* z, int ldz, const void* correction, int corr_dtype, int T, int E, int top, int n_groups, int keep,
+                     int* ids, float* wts, int score_kind, int group_top, void* stream);
+int bl_expert_gemm_plain_some(const void* x, int x_dtype, int x_div, const void* w, int w_dtype, long long expert_stride,
+                              const int* ids, void* out, int out_dtype, int P, int N, int K, int epilogue, const float* act,
+                              int n_real, void* stream);
+int bl_moe_combine_some(const float* y, const float* wts, float* out, int T, int top, int d, int add, const int* ids, int n_real,
+                        const void* x, int x_dtype, void* stream);
+int bl_moe_combine_rows_some(const float* y, const int* pos, const float* wts, float* out, int T, int top, int d, int add,
+                             const void* x, int x_dtype, void* stream);
 // The same on tensor cores: the pairs (token, chosen expert) are laid out expert by expert in tiles of `tile` rows
 // (bl_moe_plan: pos [P] the row of each pair, row_src [max_tiles * tile] the pair of each row or -1, tile_expert
 // [max_tiles] the expert of each tile or -1; max_tiles >= ceil(P / tile) + E), the tokens' rows are gathered there

@@ -7,7 +7,7 @@
 // at its first visible key. This is the 32-bit path's attention and the twin of the fast kernels.
 // Options (bl_attention_plain_ext): values of another head size than the keys; a sink per head, a learned score that
 // joins the softmax's denominator once, unscaled, without a value; a gate per (token, head) whose sigmoid multiplies
-// the head's output.
+// the head's output; a cap c on the scores, s <- c tanh(s / c), applied to the scaled score before the softmax.
 #include "common.cuh"
 #include "api.h"
 
@@ -22,7 +22,7 @@ attention_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ kc, cons
                        const int* __restrict__ tok_req, const int* __restrict__ cu_q,
                        const int* __restrict__ ctx_len, const int* __restrict__ block_table, int max_pages,
                        TT* __restrict__ out, int T, int H, int KV, int dh, int dv, int page_size, int window,
-                       float scale, const void* __restrict__ sinks, int sink_dtype, const float* gate, int ld_gate) {
+                       float scale, const void* __restrict__ sinks, int sink_dtype, const float* gate, int ld_gate, float softcap) {
     __shared__ float qs[WARPS][MAX_DH];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * WARPS + warp;
@@ -53,6 +53,7 @@ attention_plain_kernel(const TT* __restrict__ q, const TT* __restrict__ kc, cons
             float dot = 0.f;
             for (int d = 0; d < dh; ++d) dot = fmaf(qs[warp][d], bl_load(krow + d), dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float m_new = fmaxf(m, bl_warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -107,7 +108,17 @@ extern "C" int bl_attention_plain_ext(const void* q, const void* k_cache, const 
                                       const int* block_table, int max_pages, void* out, int T, int H, int KV,
                                       int dh, int dv, int page_size, int window, float scale, const void* sinks,
                                       int sink_dtype, const float* gate, int ld_gate, void* stream) {
+    return bl_attention_plain_cap(q, k_cache, v_cache, dtype, tok_req, cu_q, ctx_len, block_table, max_pages, out, T, H, KV,
+                                  dh, dv, page_size, window, scale, sinks, sink_dtype, gate, ld_gate, 0.f, stream);
+}
+
+extern "C" int bl_attention_plain_cap(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                      const int* tok_req, const int* cu_q, const int* ctx_len,
+                                      const int* block_table, int max_pages, void* out, int T, int H, int KV,
+                                      int dh, int dv, int page_size, int window, float scale, const void* sinks,
+                                      int sink_dtype, const float* gate, int ld_gate, float softcap, void* stream) {
     if (T <= 0) return 0;
+    if (!(softcap >= 0.f)) BL_FAIL("bl_attention_plain: a cap on the scores must not be negative, got %g", (double)softcap);
     if (dv <= 0 || dv > MAX_DH) BL_FAIL("bl_attention_plain: value head size %d is outside 1..%d", dv, MAX_DH);
     if (gate && ld_gate < H) BL_FAIL("bl_attention_plain: gate rows of %d hold fewer than %d heads", ld_gate, H);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("bl_attention_plain: %d heads cannot share %d key/value heads", H, KV);
@@ -118,11 +129,11 @@ extern "C" int bl_attention_plain_ext(const void* q, const void* k_cache, const 
     if (dtype == BL_F32)
         attention_plain_kernel<float><<<blocks, WARPS * 32, 0, s>>>((const float*)q, (const float*)k_cache,
             (const float*)v_cache, tok_req, cu_q, ctx_len, block_table, max_pages, (float*)out, T, H, KV, dh, dv,
-            page_size, window, scale, sinks, sink_dtype, gate, ld_gate);
+            page_size, window, scale, sinks, sink_dtype, gate, ld_gate, softcap);
     else if (dtype == BL_BF16)
         attention_plain_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, s>>>((const __nv_bfloat16*)q,
             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, tok_req, cu_q, ctx_len, block_table,
-            max_pages, (__nv_bfloat16*)out, T, H, KV, dh, dv, page_size, window, scale, sinks, sink_dtype, gate, ld_gate);
+            max_pages, (__nv_bfloat16*)out, T, H, KV, dh, dv, page_size, window, scale, sinks, sink_dtype, gate, ld_gate, softcap);
     else
         BL_FAIL("bl_attention_plain: unknown dtype %d", dtype);
     BL_CHECK_LAUNCH("bl_attention_plain");

@@ -99,6 +99,11 @@ __device__ __forceinline__ BlGluArgs bl_glu_args(const void* two_numbers) {
     return a;
 }
 
+// xIELU with ap = softplus(p) and an = 1/2 + softplus(q) made ready: v > 0: ap v^2 + v / 2; v <= 0: an (e^v - 1 - v) + v / 2.
+__device__ __forceinline__ float bl_xielu(float v, float ap, float an) {
+    return v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
+}
+
 // What may follow the softmax of an attention row: a sink per head (a learned score whose exponential joins the
 // denominator once, unscaled, with no value) and a gate per (token, head) whose sigmoid multiplies the row's output.
 // bl_attn_tail returns the factor for the row's unnormalised output, given the row's maximum m in the base-2 domain

@@ -389,6 +389,20 @@ __global__ void activation4_kernel(const float* x, TO* y, size_t count4, int col
     }
 }
 
+// xIELU with its two numbers made ready (args = {softplus(p), 1/2 + softplus(q)}, 32-bit on the device):
+// v > 0: args[0] v^2 + v / 2;  v <= 0: args[1] (e^v - 1 - v) + v / 2. x: 32-bit sums.
+template <typename TO>
+__global__ void xielu_kernel(const float* x, TO* y, size_t count, int cols, size_t ld_x, size_t ld_y, const float* __restrict__ args) {
+    bl_pdl_trigger();
+    const float ap = args[0], an = args[1];
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / cols, c = e % cols;
+        const float v = x[r * ld_x + c];
+        bl_store(y + r * ld_y + c, bl_xielu(v, ap, an));
+    }
+}
+
 int grid_for(size_t count, int threads) {
     size_t b = (count + threads - 1) / threads;
     return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -540,5 +554,19 @@ extern "C" int bl_norm_chain(float* x, const float* sub, const float* gate, int 
     else
         BL_FAIL("bl_norm_chain: unknown output dtype %d", y_dtype);
     BL_CHECK_LAUNCH("bl_norm_chain");
+    return 0;
+}
+
+extern "C" int bl_xielu(const float* x, long long ld_x, void* y, int y_dtype, long long ld_y, int rows, int cols, const float* args,
+                        void* stream) {
+    const long long count = (long long)rows * cols;
+    if (count <= 0) return 0;
+    if (ld_x < cols || ld_y < cols || !args) BL_FAIL("bl_xielu: rows of %d values are %lld and %lld apart", cols, ld_x, ld_y);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int g = grid_for((size_t)count, 256);
+    if (y_dtype == BL_F32) BL_CUDA(bl_launch_dependent(xielu_kernel<float>, dim3(g), dim3(256), 0, s, x, (float*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, args));
+    else if (y_dtype == BL_BF16) BL_CUDA(bl_launch_dependent(xielu_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, s, x, (__nv_bfloat16*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, args));
+    else BL_FAIL("bl_xielu: unknown dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_xielu");
     return 0;
 }

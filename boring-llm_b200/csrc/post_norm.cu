@@ -138,6 +138,22 @@ pair_rms_mean_kernel(const float* a, const void* __restrict__ wa, int wa_dtype, 
         out[(size_t)r * d + i] = 0.5f * (ar[i] * inv_a * bl_load_any(wa, wa_dtype, i) + br[i] * inv_b * bl_load_any(wb, wb_dtype, i));
 }
 
+// x += ca * a + cb * b, element by element (32-bit): two sublayer results that join the stream with a constant factor each.
+__global__ void add_scaled_pair_kernel(float* x, const float* a, float ca, const float* b, float cb, size_t count) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x)
+        x[e] += fmaf(ca, a[e], cb * b[e]);
+}
+
+// x[r, :] += sigmoid(g[r * ld_g]) * a[r, :]: a sublayer result behind a gate of ONE number per row.
+__global__ void add_row_gated_kernel(float* x, const float* a, const float* g, size_t ld_g, int d, size_t count) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x)
+        x[e] = fmaf(1.0f / (1.0f + expf(-g[(e / d) * ld_g])), a[e], x[e]);
+}
+
 template <typename TY>
 __global__ void cast_rows_kernel(const float* x, TY* y, size_t count) {
     bl_pdl_trigger();
@@ -213,5 +229,25 @@ extern "C" int bl_softcap(float* x, long long count, float cap, void* stream) {
     const int blocks = (int)((count + 1023) / 1024 < 2048 ? (count + 1023) / 1024 : 2048);
     BL_CUDA(bl_launch_dependent(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)count, cap, 1.0f / cap));
     BL_CHECK_LAUNCH("bl_softcap");
+    return 0;
+}
+
+extern "C" int bl_add_scaled_pair(float* x, const float* a, float ca, const float* b, float cb, long long count, void* stream) {
+    if (count <= 0) return 0;
+    if (!x || !a || !b) BL_FAIL("bl_add_scaled_pair: a null operand");
+    const int blocks = (int)((count + 1023) / 1024 < 2048 ? (count + 1023) / 1024 : 2048);
+    BL_CUDA(bl_launch_dependent(add_scaled_pair_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, a, ca, b, cb, (size_t)count));
+    BL_CHECK_LAUNCH("bl_add_scaled_pair");
+    return 0;
+}
+
+extern "C" int bl_add_row_gated(float* x, const float* a, const float* gate, long long ld_gate, int rows, int d, void* stream) {
+    if (rows <= 0) return 0;
+    if (!x || !a || !gate || d <= 0 || ld_gate < 1) BL_FAIL("bl_add_row_gated: bad arguments (d=%d)", d);
+    const long long count = (long long)rows * d;
+    const int blocks = (int)((count + 1023) / 1024 < 2048 ? (count + 1023) / 1024 : 2048);
+    BL_CUDA(bl_launch_dependent(add_row_gated_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, a, gate, (size_t)ld_gate, d,
+                                (size_t)count));
+    BL_CHECK_LAUNCH("bl_add_row_gated");
     return 0;
 }

@@ -465,7 +465,7 @@ head_norm_gate_kernel(const float* o, int o_head_stride, const void* __restrict_
     const float* g = gate ? gate + (size_t)t * ld_gate + h * dv : nullptr;
     const size_t w0 = w_per_head ? (size_t)h * dv : 0;
     for (int i = lane; i < dv; i += 32) {
-        float val = src[i] * inv * bl_load_any(w, w_dtype, w0 + i);
+        float val = src[i] * inv * (w ? bl_load_any(w, w_dtype, w0 + i) : 1.f);
         if (g) val *= gate_kind == BL_GATE_SILU ? bl_silu(g[i]) : sigmoidf_(g[i]);
         bl_store(y + (size_t)item * dv + i, val);
     }
@@ -603,7 +603,8 @@ bonus_dot_kernel(const float* q, int ldq, const float* k, int ldk, const void* _
 __global__ void __launch_bounds__(WARPS * 32)
 conv_silu_unit_kernel(const float* x, int ld, const float* __restrict__ taps, int n_taps, const float* tail, size_t slot_stride,
                       const int* __restrict__ slots, const int* __restrict__ tok_req, const int* __restrict__ cu_q, float* y,
-                      int C, int unit_heads, int scaled_heads, int dk, float q_scale, float unit_eps) {
+                      int C, int unit_heads, int scaled_heads, int dk, float q_scale, float unit_eps, const void* __restrict__ bias,
+                      int bias_dtype) {
     bl_pdl_trigger();
     bl_pdl_wait();
     const int t = blockIdx.x;
@@ -611,7 +612,7 @@ conv_silu_unit_kernel(const float* x, int ld, const float* __restrict__ taps, in
     const int j = t - cu_q[r];
     const float* tl = tail + (size_t)slots[r] * slot_stride;
     for (int ch = threadIdx.x; ch < C; ch += WARPS * 32) {
-        float acc = 0.f;
+        float acc = bias ? bl_load_any(bias, bias_dtype, ch) : 0.f;
         for (int i = 0; i < n_taps; ++i) {
             const int off = j - (n_taps - 1) + i;
             const float xv = off >= 0 ? x[(size_t)(t - j + off) * ld + ch] : tl[(size_t)(n_taps - 1 + off) * C + ch];
@@ -651,6 +652,96 @@ __global__ void conv_tail_update_kernel(const float* x, int ld, int n_taps, floa
 #pragma unroll
     for (int i = 0; i < MAX_TAPS; ++i)
         if (i < n_taps - 1) tl[(size_t)i * C + ch] = keep[i];
+}
+
+
+// In front of a recurrence with a FIXED decay per head (retention): q and k of every head rotated by the token's position
+// (the first 2 * rot_half values of a head in pairs (i, i + rot_half), angle = float(position) * inv_freq[i], all 32-bit),
+// k times k_scale after the rotation, and the head's decay written for each of its key channels (what the scan reads).
+// One block per token.
+__global__ void __launch_bounds__(WARPS * 32)
+rope_decay_prep_kernel(const float* proj, int ld, int off_k, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                       int rot_half, const float* __restrict__ head_decay, float k_scale, float* q_out, float* k_out,
+                       float* decay_out, int H, int dk) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    const float* src = proj + (size_t)t * ld;
+    const size_t row = (size_t)t * H * dk;
+    for (int e = threadIdx.x; e < H * dk; e += WARPS * 32) {
+        const int h = e / dk, d = e % dk;
+        float qv = src[e], kv = src[off_k + e];
+        if (d < 2 * rot_half) {
+            const int i = d < rot_half ? d : d - rot_half;
+            float sn, cs;
+            sincosf(pos * inv_freq[i], &sn, &cs);
+            const int other = d < rot_half ? e + rot_half : e - rot_half;
+            const float qo = src[other], ko = src[off_k + other];
+            if (d < rot_half) { qv = qv * cs - qo * sn; kv = kv * cs - ko * sn; }
+            else { qv = qv * cs + qo * sn; kv = kv * cs + ko * sn; }
+        }
+        q_out[row + e] = qv;
+        k_out[row + e] = kv * k_scale;
+        decay_out[row + e] = head_decay[h];
+    }
+}
+
+// In front of a selective state-space recurrence (one decay per head and token): dt = softplus(raw + dt_bias[h]);
+// decay[t, h, :] = exp(-exp(A_log[h]) * dt) for each of the n_state key channels; v[t, h, :] = dt * x[t, h, :].
+// raw: 32-bit rows [T, >= H]; x: [T, H * dv] (the convolved inputs). neg_rate[h] = exp(A_log[h]), made at load. One block per token.
+__global__ void __launch_bounds__(WARPS * 32)
+ssd_prep_kernel(const float* raw, int ld_raw, const void* __restrict__ dt_bias, int bias_dtype, const float* __restrict__ rate,
+                const float* x, int ld_x, float* decay_out, float* v_out, int H, int n_state, int dv) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    __shared__ float dts[256];
+    const int t = blockIdx.x;
+    for (int h0 = 0; h0 < H; h0 += 256) {
+        const int hn = min(256, H - h0);
+        __syncthreads();
+        for (int h = threadIdx.x; h < hn; h += WARPS * 32) {
+            const float zz = raw[(size_t)t * ld_raw + h0 + h] + bl_load_any(dt_bias, bias_dtype, h0 + h);
+            dts[h] = zz > 20.f ? zz : log1pf(expf(zz));
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < hn * n_state; e += WARPS * 32) {
+            const int h = e / n_state;
+            decay_out[((size_t)t * H + h0) * n_state + e] = expf(-rate[h0 + h] * dts[h]);
+        }
+        for (int e = threadIdx.x; e < hn * dv; e += WARPS * 32) {
+            const int h = e / dv;
+            v_out[((size_t)t * H + h0) * dv + e] = dts[h] * x[(size_t)t * ld_x + (size_t)h0 * dv + e];
+        }
+    }
+}
+
+// Behind such a recurrence: u = (o + skip[h] * x) * silu(z) (the gate comes BEFORE the norm), then an RMS norm over each of
+// n_parts equal parts of the row (each part by its own root mean square), times w. One warp per (token, part); a part may
+// span several heads or a fraction of one. skip and x may be null (no skip term), z may be null (no gate).
+template <typename TY>
+__global__ void __launch_bounds__(WARPS * 32)
+gated_group_norm_kernel(const float* o, const float* x, int ld_x, const void* __restrict__ skip, int skip_dtype, int dv,
+                        const float* z, int ld_z, const void* __restrict__ w, int w_dtype, TY* __restrict__ y, int items, int n_parts,
+                        int width, float eps) {
+    bl_pdl_trigger();
+    bl_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * WARPS + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int t = item / n_parts, part = item % n_parts;
+    const int per = width / n_parts, c0 = part * per;
+    auto value = [&](int c) {
+        float u = o[(size_t)t * width + c];
+        if (x) u = fmaf(bl_load_any(skip, skip_dtype, c / dv), x[(size_t)t * ld_x + c], u);
+        if (z) u *= bl_silu(z[(size_t)t * ld_z + c]);
+        return u;
+    };
+    float ss = 0.f;
+    for (int i = lane; i < per; i += 32) { const float u = value(c0 + i); ss += u * u; }
+    const float inv = 1.0f / sqrtf(bl_warp_sum(ss) / (float)per + eps);
+    for (int i = lane; i < per; i += 32)
+        bl_store(y + (size_t)t * width + c0 + i, value(c0 + i) * inv * (w ? bl_load_any(w, w_dtype, c0 + i) : 1.f));
 }
 
 }  // namespace
@@ -836,12 +927,21 @@ extern "C" int bl_bonus_dot(const float* q, int ldq, const float* k, int ldk, co
 extern "C" int bl_conv_silu_unit(const float* x, int ld, const float* taps, int n_taps, const float* tail, long long slot_stride,
                                  const int* slots, const int* tok_req, const int* cu_q, float* y, int T, int C, int unit_heads,
                                  int scaled_heads, int dk, float q_scale, float unit_eps, void* stream) {
+    return bl_conv_silu_unit_bias(x, ld, taps, n_taps, tail, slot_stride, slots, tok_req, cu_q, y, T, C, unit_heads, scaled_heads, dk,
+                                  q_scale, unit_eps, nullptr, BL_F32, stream);
+}
+
+// The same with a bias per channel (null: none) that the convolution's sum starts from.
+extern "C" int bl_conv_silu_unit_bias(const float* x, int ld, const float* taps, int n_taps, const float* tail, long long slot_stride,
+                                      const int* slots, const int* tok_req, const int* cu_q, float* y, int T, int C, int unit_heads,
+                                      int scaled_heads, int dk, float q_scale, float unit_eps, const void* bias, int bias_dtype,
+                                      void* stream) {
     if (T <= 0) return 0;
     if (n_taps < 1 || n_taps > MAX_TAPS) BL_FAIL("bl_conv_silu_unit: %d taps, 1..%d are built", n_taps, MAX_TAPS);
     if (C <= 0 || ld < C || unit_heads * dk > C || scaled_heads > unit_heads)
         BL_FAIL("bl_conv_silu_unit: bad sizes C=%d ld=%d heads=%d of %d", C, ld, unit_heads, dk);
     BL_CUDA(bl_launch_dependent(conv_silu_unit_kernel, dim3(T), dim3(WARPS * 32), 0, (cudaStream_t)stream, x, ld, taps, n_taps, tail,
-                                (size_t)slot_stride, slots, tok_req, cu_q, y, C, unit_heads, scaled_heads, dk, q_scale, unit_eps));
+                                (size_t)slot_stride, slots, tok_req, cu_q, y, C, unit_heads, scaled_heads, dk, q_scale, unit_eps, bias, bias_dtype));
     BL_CHECK_LAUNCH("bl_conv_silu_unit");
     return 0;
 }
@@ -855,5 +955,49 @@ extern "C" int bl_conv_tail_update(const float* x, int ld, int n_taps, float* ta
     BL_CUDA(bl_launch_dependent(conv_tail_update_kernel, grid, dim3(128), 0, (cudaStream_t)stream, x, ld, n_taps, tail,
                                 (size_t)slot_stride, slots, cu_q, C));
     BL_CHECK_LAUNCH("bl_conv_tail_update");
+    return 0;
+}
+
+extern "C" int bl_rope_decay_prep(const float* proj, int ld, int off_k, const int* positions, const float* inv_freq, int rot_half,
+                                  const float* head_decay, float k_scale, float* q_out, float* k_out, float* decay_out, int T, int H,
+                                  int dk, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || dk <= 0 || rot_half < 0 || 2 * rot_half > dk || off_k < H * dk || ld < off_k + H * dk)
+        BL_FAIL("bl_rope_decay_prep: bad sizes H=%d dk=%d rotated pairs=%d off_k=%d ld=%d", H, dk, rot_half, off_k, ld);
+    BL_CUDA(bl_launch_dependent(rope_decay_prep_kernel, dim3(T), dim3(WARPS * 32), 0, (cudaStream_t)stream, proj, ld, off_k, positions,
+                                inv_freq, rot_half, head_decay, k_scale, q_out, k_out, decay_out, H, dk));
+    BL_CHECK_LAUNCH("bl_rope_decay_prep");
+    return 0;
+}
+
+extern "C" int bl_ssd_prep(const float* raw, int ld_raw, const void* dt_bias, int bias_dtype, const float* rate, const float* x,
+                           int ld_x, float* decay_out, float* v_out, int T, int H, int n_state, int dv, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || n_state <= 0 || dv <= 0 || ld_raw < H || ld_x < H * dv)
+        BL_FAIL("bl_ssd_prep: bad sizes H=%d state=%d dv=%d ld_raw=%d ld_x=%d", H, n_state, dv, ld_raw, ld_x);
+    BL_CUDA(bl_launch_dependent(ssd_prep_kernel, dim3(T), dim3(WARPS * 32), 0, (cudaStream_t)stream, raw, ld_raw, dt_bias, bias_dtype,
+                                rate, x, ld_x, decay_out, v_out, H, n_state, dv));
+    BL_CHECK_LAUNCH("bl_ssd_prep");
+    return 0;
+}
+
+extern "C" int bl_gated_group_norm(const float* o, const float* x, int ld_x, const void* skip, int skip_dtype, int dv, const float* z,
+                                   int ld_z, const void* w, int w_dtype, void* y, int y_dtype, int T, int width, int n_parts, float eps,
+                                   void* stream) {
+    if (T <= 0) return 0;
+    if (width <= 0 || n_parts <= 0 || width % n_parts != 0 || (x && (dv <= 0 || width % dv != 0 || ld_x < width || !skip)) ||
+        (z && ld_z < width))
+        BL_FAIL("bl_gated_group_norm: bad sizes width=%d parts=%d dv=%d ld_x=%d ld_z=%d", width, n_parts, dv, ld_x, ld_z);
+    const int items = T * n_parts, blocks = (items + WARPS - 1) / WARPS;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype == BL_F32)
+        BL_CUDA(bl_launch_dependent(gated_group_norm_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, s, o, x, ld_x, skip, skip_dtype, dv, z,
+                                    ld_z, w, w_dtype, (float*)y, items, n_parts, width, eps));
+    else if (y_dtype == BL_BF16)
+        BL_CUDA(bl_launch_dependent(gated_group_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, s, o, x, ld_x, skip, skip_dtype,
+                                    dv, z, ld_z, w, w_dtype, (__nv_bfloat16*)y, items, n_parts, width, eps));
+    else
+        BL_FAIL("bl_gated_group_norm: unknown output dtype %d", y_dtype);
+    BL_CHECK_LAUNCH("bl_gated_group_norm");
     return 0;
 }

@@ -260,8 +260,9 @@ def qkv_rope_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
 def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tok_req: torch.Tensor,
                     cu_q: torch.Tensor, ctx_len: torch.Tensor, block_table: torch.Tensor,
                     out: torch.Tensor, H: int, window: int, scale: float, sinks: Optional[torch.Tensor] = None,
-                    gate: Optional[torch.Tensor] = None) -> None:
-    """Paged causal grouped-query attention, one warp per (token, head). The values' head size may differ from the
+                    gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
+    """Paged causal grouped-query attention, one warp per (token, head). `softcap` c > 0: the scaled scores pass
+    c * tanh(s / c) before the softmax. The values' head size may differ from the
     keys' (v_cache `[pages, kv heads, page, dv]`, out `[T, H * dv]`). `sinks` [H]: exp(sinks[h]) joins head h's softmax
     denominator (once, unscaled, no value). `gate` (32-bit, [T, >= H], rows contiguous, possibly a column range of a
     wider matrix): head h of token t is multiplied by sigmoid(gate[t, h])."""
@@ -279,9 +280,10 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if not gate.is_cuda or gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < H:
             raise KernelError("gate: must be 32-bit CUDA rows [T, >= H] with contiguous rows")
         ld_gate = gate.stride(0)
-    _call(_lib().bl_attention_plain_ext, _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(tok_req), _p(cu_q),
+    _call(_lib().bl_attention_plain_cap, _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(tok_req), _p(cu_q),
           _p(ctx_len), _p(block_table), block_table.shape[1], _p(out), T, H, KV, dh, dv, page_size, window,
-          ctypes.c_float(scale), _p(sinks), _dt(sinks) if sinks is not None else 0, _p(gate), ld_gate, _stream())
+          ctypes.c_float(scale), _p(sinks), _dt(sinks) if sinks is not None else 0, _p(gate), ld_gate, ctypes.c_float(softcap),
+          _stream())
 
 
 def argmax(logits: torch.Tensor, out_ids: torch.Tensor) -> None:
@@ -968,19 +970,21 @@ def recurrent_scan(rule: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
           _p(out), H, G, dk, dv, _stream())
 
 
-def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], gate_kind: int, eps: float,
+def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], gate_kind: int, eps: float,
                    out: torch.Tensor, H: int, dv: int) -> None:
     """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * g(gate[t, h]), g = sigmoid or silu (gate None: 1)."""
     T = o.shape[0]
-    _need(o, "o", torch.float32, (T, H * dv)); _need(weight, "weight", None, (dv,)); _need(out, "out", None, (T, H * dv))
+    _need(o, "o", torch.float32, (T, H * dv)); _need(out, "out", None, (T, H * dv))
+    if weight is not None:                   # None: the norm has no weight
+        _need(weight, "weight", None, (dv,))
     ld = _rows32(gate, "gate", T, H * dv) if gate is not None else 0
-    _call(_lib().bl_head_norm_gate, _p(o), _p(weight), _dt(weight), _p(gate), ld, gate_kind, _p(out), _dt(out), T, H, dv,
+    _call(_lib().bl_head_norm_gate, _p(o), _p(weight), _vec_dt(weight), _p(gate), ld, gate_kind, _p(out), _dt(out), T, H, dv,
           ctypes.c_float(eps), _stream())
 
 
 def conv_silu_unit(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, slots: torch.Tensor, tok_req: torch.Tensor,
                    cu_q: torch.Tensor, out: torch.Tensor, unit_heads: int, scaled_heads: int, dk: int, q_scale: float,
-                   unit_eps: float) -> None:
+                   unit_eps: float, bias: Optional[torch.Tensor] = None) -> None:
     """out = silu(short causal convolution of x over a request's tokens, per channel), then the first `unit_heads` heads
     of dk columns made unit vectors (the first `scaled_heads` times q_scale). x: 32-bit rows [T, >= C]; taps [C, n]
     32-bit (the last column is the current token's); tail: [slots, >= (n - 1) * C] 32-bit rows (a column range of the
@@ -992,9 +996,11 @@ def conv_silu_unit(x: torch.Tensor, taps: torch.Tensor, tail: torch.Tensor, slot
     _need(slots, "slots", torch.int32); _need(tok_req, "tok_req", torch.int32, (T,)); _need(cu_q, "cu_q", torch.int32)
     if not tail.is_cuda or tail.dtype != torch.float32 or tail.stride(1) != 1 or tail.shape[1] < (n_taps - 1) * C:
         raise KernelError("tail: must be 32-bit [slots, >= (taps - 1) * C] with contiguous rows")
-    _call(_lib().bl_conv_silu_unit, _p(x), ld, _p(taps), n_taps, _p(tail), ctypes.c_longlong(tail.stride(0)), _p(slots),
+    if bias is not None:                     # a bias per channel that the convolution's sum starts from
+        _need(bias, "bias", None, (C,))
+    _call(_lib().bl_conv_silu_unit_bias, _p(x), ld, _p(taps), n_taps, _p(tail), ctypes.c_longlong(tail.stride(0)), _p(slots),
           _p(tok_req), _p(cu_q), _p(out), T, C, unit_heads, scaled_heads, dk, ctypes.c_float(q_scale), ctypes.c_float(unit_eps),
-          _stream())
+          _p(bias), _vec_dt(bias), _stream())
 
 
 def conv_tail_update(x: torch.Tensor, n_taps: int, tail: torch.Tensor, slots: torch.Tensor, cu_q: torch.Tensor, C: int) -> None:
@@ -1258,15 +1264,21 @@ def bonus_dot(q: torch.Tensor, k: torch.Tensor, u: torch.Tensor, out: torch.Tens
     _call(_lib().bl_bonus_dot, _p(q), ldq, _p(k), ldk, _p(u), _dt(u), _p(out), T, H, dk, _stream())
 
 
+SCORE_SIGMOID, SCORE_SOFTMAX = 0, 1
+
+
 def moe_route(z: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int, keep: int, ids: torch.Tensor,
-              wts: torch.Tensor) -> None:
-    """The experts of each token and their weights from the router's 32-bit logits z [T, E] (see `bl_moe_route`)."""
+              wts: torch.Tensor, score: int = SCORE_SIGMOID, group_top: int = 2) -> None:
+    """The experts of each token and their weights from the router's 32-bit logits z [T, E] (see `bl_moe_route`). `score`:
+    sigmoid of each logit, or the softmax over all E; `group_top`: a group's score is the sum of its two largest choice
+    scores (2) or its largest (1)."""
     T, E = z.shape
     ld = _rows32(z, "z", T, E)
     if correction is not None:
         _need(correction, "correction", None, (E,))
     _need(ids, "ids", torch.int32, (T, top)); _need(wts, "wts", torch.float32, (T, top))
-    _call(_lib().bl_moe_route, _p(z), ld, _p(correction), _vec_dt(correction), T, E, top, n_groups, keep, _p(ids), _p(wts), _stream())
+    _call(_lib().bl_moe_route_ext, _p(z), ld, _p(correction), _vec_dt(correction), T, E, top, n_groups, keep, _p(ids), _p(wts),
+          score, group_top, _stream())
 
 
 def expert_gemm_plain(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
@@ -1284,16 +1296,22 @@ def expert_gemm_plain(x: torch.Tensor, x_div: int, w: torch.Tensor, ids: torch.T
     rows_w = 2 * N if epilogue == EPI_SWIGLU else N
     if w.dim() != 3 or w.shape[1] != rows_w or w.shape[2] != K or ids.numel() != P or x.shape[0] * x_div != P:
         raise KernelError(f"expert_gemm_plain: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, {ids.numel()} ids do not fit")
-    _call(_lib().bl_expert_gemm_plain, _p(x), _dt(x), x_div, _p(w), _dt(w), ctypes.c_longlong(w.stride(0)), _p(ids), _p(out), _dt(out),
-          P, N, K, epilogue, _p(act), _stream())
+    # (ids beyond w's experts are identity experts: their rows are skipped)
+    _call(_lib().bl_expert_gemm_plain_some, _p(x), _dt(x), x_div, _p(w), _dt(w), ctypes.c_longlong(w.stride(0)), _p(ids), _p(out), _dt(out),
+          P, N, K, epilogue, _p(act), w.shape[0], _stream())
 
 
-def moe_combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:
-    """out[t] = sum_k wts[t, k] * y[t * top + k], k ascending (32-bit); with `add` the sum is added to out."""
+def moe_combine(y: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False, ids: Optional[torch.Tensor] = None,
+                n_real: int = 0, x: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_k wts[t, k] * y[t * top + k], k ascending (32-bit); with `add` the sum is added to out. With `ids`, a pair
+    whose expert number is `n_real` or more is an identity expert and contributes x[t] (the token's input row) instead."""
     T, top = wts.shape
     d = out.shape[1]
     _need(y, "y", torch.float32, (T * top, d)); _need(wts, "wts", torch.float32); _need(out, "out", torch.float32, (T, d))
-    _call(_lib().bl_moe_combine, _p(y), _p(wts), _p(out), T, top, d, 1 if add else 0, _stream())
+    if ids is not None:
+        _need(ids, "ids", torch.int32, (T, top)); _need(x, "x", None, (T, d))
+    _call(_lib().bl_moe_combine_some, _p(y), _p(wts), _p(out), T, top, d, 1 if add else 0, _p(ids), n_real, _p(x),
+          _dt(x) if x is not None else 0, _stream())
 
 
 GROUPED_TILE = 128         # rows of a tile of the grouped tensor-core product (every expert's rows start a new tile)
@@ -1308,7 +1326,8 @@ def grouped_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 def moe_plan(ids: torch.Tensor, n_experts: int):
     """The layout of the pairs (token, chosen expert) for the grouped product: (pos [P] the row of each pair, row_src
     [rows] the pair of each row or -1, tile_expert [tiles] the expert of each tile of 128 rows or -1). The number of
-    rows depends on the number of pairs and experts only (every expert may leave one tile partly empty)."""
+    rows depends on the number of pairs and experts only (every expert may leave one tile partly empty). Pairs whose expert
+    number is `n_experts` or more (identity experts) get no row: their pos is -1."""
     P = ids.numel()
     tiles = -(-P // GROUPED_TILE) + n_experts
     _need(ids, "ids", torch.int32)
@@ -1342,14 +1361,19 @@ def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, ou
     _call(_lib().bl_gemm_tc_grouped, _p(x), _p(w), _p(out), _dt(out), M, N, K, epilogue, E, _p(tile_expert), _p(act), _stream())
 
 
-def moe_combine_rows(y: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:
-    """out[t] = sum_k wts[t, k] * y[pos[t * top + k]], k ascending (32-bit); with `add` the sum is added to out."""
+def moe_combine_rows(y: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, add: bool = False,
+                     x: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_k wts[t, k] * y[pos[t * top + k]], k ascending (32-bit); with `add` the sum is added to out. A pair without
+    a row (pos < 0: an identity expert, see `moe_plan`) contributes x[t], the token's input row."""
     T, top = wts.shape
     d = out.shape[1]
     _need(y, "y", torch.float32); _need(pos, "pos", torch.int32, (T * top,)); _need(wts, "wts", torch.float32); _need(out, "out", torch.float32, (T, d))
     if y.shape[1] != d:
         raise KernelError("moe_combine_rows: y and out differ in width")
-    _call(_lib().bl_moe_combine_rows, _p(y), _p(pos), _p(wts), _p(out), T, top, d, 1 if add else 0, _stream())
+    if x is not None:
+        _need(x, "x", None, (T, d))
+    _call(_lib().bl_moe_combine_rows_some, _p(y), _p(pos), _p(wts), _p(out), T, top, d, 1 if add else 0, _p(x),
+          _dt(x) if x is not None else 0, _stream())
 
 
 GLU_SILU, GLU_GELU_TANH, GLU_CLAMPED = 0, 1, 2
@@ -1529,3 +1553,80 @@ def heads_gate_rows(hv: torch.Tensor, gate: Optional[torch.Tensor], out: torch.T
     _need(hv, "hv", torch.float32); _need(out, "out", None, (T, H * N))
     ld = _rows32(gate, "gate", T, H * N) if gate is not None else 0
     _call(_lib().bl_heads_gate_rows, _p(hv), _p(gate), ctypes.c_longlong(ld), _p(out), _dt(out), T, H, N, Tp, _stream())
+
+
+def rope_decay_prep(proj: torch.Tensor, off_k: int, positions: torch.Tensor, inv_freq: torch.Tensor, rot_half: int,
+                    head_decay: torch.Tensor, k_scale: float, H: int, dk: int):
+    """In front of a recurrence with a fixed decay per head: (q, k, decay), each 32-bit [T, H * dk], from the joined
+    projections (q first, k from column off_k): q and k rotated by position (pairs (i, i + rot_half) of each head's first
+    2 * rot_half values, 32-bit angles), k times k_scale, decay[t, h, :] = head_decay[h]."""
+    T = proj.shape[0]
+    ld = _rows32(proj, "proj", T, off_k + H * dk)
+    _need(positions, "positions", torch.int32, (T,)); _need(inv_freq, "inv_freq", torch.float32); _need(head_decay, "head_decay", torch.float32, (H,))
+    if inv_freq.numel() < rot_half:
+        raise KernelError("inv_freq: fewer entries than rotated pairs")
+    q, k, decay = (torch.empty((T, H * dk), dtype=torch.float32, device=proj.device) for _ in range(3))
+    _call(_lib().bl_rope_decay_prep, _p(proj), ld, off_k, _p(positions), _p(inv_freq), rot_half, _p(head_decay), ctypes.c_float(k_scale),
+          _p(q), _p(k), _p(decay), T, H, dk, _stream())
+    return q, k, decay
+
+
+def ssd_prep(raw: torch.Tensor, dt_bias: torch.Tensor, rate: torch.Tensor, x: torch.Tensor, H: int, n_state: int, dv: int):
+    """In front of a selective state-space recurrence: dt = softplus(raw + dt_bias) per (token, head), 32-bit; returns
+    (decay [T, H * n_state] = exp(-rate[h] * dt) for every key channel, v [T, H * dv] = dt * x). raw [T, >= H] and x
+    [T, >= H * dv] are 32-bit rows, possibly column ranges of wider matrices."""
+    T = raw.shape[0]
+    ld_raw, ld_x = _rows32(raw, "raw", T, H), _rows32(x, "x", T, H * dv)
+    _need(dt_bias, "dt_bias", None, (H,)); _need(rate, "rate", torch.float32, (H,))
+    decay = torch.empty((T, H * n_state), dtype=torch.float32, device=raw.device)
+    v = torch.empty((T, H * dv), dtype=torch.float32, device=raw.device)
+    _call(_lib().bl_ssd_prep, _p(raw), ld_raw, _p(dt_bias), _dt(dt_bias), _p(rate), _p(x), ld_x, _p(decay), _p(v), T, H, n_state, dv, _stream())
+    return decay, v
+
+
+def gated_group_norm(o: torch.Tensor, x: Optional[torch.Tensor], skip: Optional[torch.Tensor], dv: int, z: Optional[torch.Tensor],
+                     weight: Optional[torch.Tensor], n_parts: int, eps: float, out: torch.Tensor) -> None:
+    """out = rms_norm_in_parts((o + skip[c // dv] * x) * silu(z)) * weight: the gate stands IN FRONT of the norm, and each of
+    `n_parts` equal parts of a row is normed by its own root mean square. o [T, width] 32-bit; x, z: 32-bit rows (column
+    ranges allowed); x with skip, z and weight may each be None."""
+    T, width = o.shape
+    _need(o, "o", torch.float32); _need(out, "out", None, (T, width))
+    ld_x = _rows32(x, "x", T, width) if x is not None else 0
+    ld_z = _rows32(z, "z", T, width) if z is not None else 0
+    if x is not None:
+        _need(skip, "skip", None, (width // dv,))
+    if weight is not None:
+        _need(weight, "weight", None, (width,))
+    _call(_lib().bl_gated_group_norm, _p(o), _p(x), ld_x, _p(skip), _vec_dt(skip), dv, _p(z), ld_z, _p(weight), _vec_dt(weight),
+          _p(out), _dt(out), T, width, n_parts, ctypes.c_float(eps), _stream())
+
+
+def add_scaled_pair(x: torch.Tensor, a: torch.Tensor, ca: float, b: torch.Tensor, cb: float) -> None:
+    """x += ca * a + cb * b (32-bit): two sublayer results that join the stream with a constant factor each."""
+    _need(x, "x", torch.float32); _need(a, "a", torch.float32, tuple(x.shape)); _need(b, "b", torch.float32, tuple(x.shape))
+    _call(_lib().bl_add_scaled_pair, _p(x), _p(a), ctypes.c_float(ca), _p(b), ctypes.c_float(cb), ctypes.c_longlong(x.numel()), _stream())
+
+
+def add_row_gated(x: torch.Tensor, a: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[r] += sigmoid(gate[r, 0]) * a[r] (32-bit; gate: rows of a 32-bit matrix, its first column the logit)."""
+    rows, d = x.shape
+    _need(x, "x", torch.float32); _need(a, "a", torch.float32, (rows, d))
+    ld = _rows32(gate, "gate", rows, 1)
+    _call(_lib().bl_add_row_gated, _p(x), _p(a), _p(gate), ctypes.c_longlong(ld), rows, d, _stream())
+
+
+def xielu_args(p: float, q: float, device) -> torch.Tensor:
+    """The two numbers the xIELU kernel reads, from the learned p and q: {softplus(p), 1/2 + softplus(q)}, 32-bit."""
+    sp = lambda v: float(torch.nn.functional.softplus(torch.tensor(v, dtype=torch.float64)))
+    return torch.tensor([sp(p), 0.5 + sp(q)], dtype=torch.float32, device=device)
+
+
+def xielu(x: torch.Tensor, out: torch.Tensor, args: torch.Tensor) -> None:
+    """out = xIELU(x) on 32-bit sums (rows contiguous; column ranges allowed): v > 0: args[0] v^2 + v / 2, else
+    args[1] (e^v - 1 - v) + v / 2."""
+    rows, cols = out.shape
+    ld = _rows32(x, "x", rows, cols)
+    _need(args, "args", torch.float32, (2,))
+    if out.stride(1) != 1:
+        raise KernelError("xielu: out must have contiguous rows")
+    _call(_lib().bl_xielu, _p(x), ctypes.c_longlong(ld), _p(out), _dt(out), ctypes.c_longlong(out.stride(0)), rows, cols, _p(args), _stream())

@@ -1,5 +1,5 @@
 """Architectures of this engine. Importing the package registers them."""
-from . import qwen2, fezopel, kavotar, miforax
+from . import qwen2, fezopel, kavotar, miforax, dapuzen
 from .loading import build_model, load_model, load_random_model, write_random_model
 
-__all__ = ["qwen2", "fezopel", "kavotar", "miforax", "build_model", "load_model", "load_random_model", "write_random_model"]
+__all__ = ["qwen2", "fezopel", "kavotar", "miforax", "dapuzen", "build_model", "load_model", "load_random_model", "write_random_model"]

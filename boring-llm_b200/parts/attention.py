@@ -67,16 +67,18 @@ def attention_plan(q_lens, ctx_lens, filler=None) -> StepPlan:
 
 
 def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: int, window: int, scale: float,
-                    sinks=None, gate=None) -> None:
+                    sinks=None, gate=None, softcap: float = 0.0) -> None:
     """Causal attention of the step's tokens over the paged cache. Tensor-core kernels for bfloat16 where they are built
     (pages of 16, common head sizes, values of the keys' head size): one launch for the requests with several new tokens
     (the tcgen05 kernel for head sizes 64 and 128 when the step has many of them), one for those with a single token.
     Otherwise, and always in float32, the plain kernel. Which requests those are comes from the step's plan
     (`attention_plan`). `sinks` [H] and `gate` (32-bit logits [T, >= H]) are what may follow the softmax: a score per
-    head that joins the denominator, a sigmoid per (token, head) on the output."""
+    head that joins the denominator, a sigmoid per (token, head) on the output. `softcap` c > 0: scaled scores pass
+    c tanh(s / c) before the softmax (the plain kernel has it)."""
     dv = v_cache.shape[3]
-    if not (ctx.fast and dv == dh and ops.attention_mma_supported(q.dtype, dh, k_cache.shape[2])):
-        ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, H, window, scale, sinks, gate)
+    if not (ctx.fast and dv == dh and softcap == 0.0 and ops.attention_mma_supported(q.dtype, dh, k_cache.shape[2])):
+        ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, H, window, scale, sinks, gate,
+                            softcap=softcap)
         return
     plan = ctx.plans.get(PLAN_KEY)
     if plan is None:                                 # a step put together without asking the parts: plan it now
@@ -281,7 +283,9 @@ class GatedSinkAttention(Mixer):
     * `sink=True`: a learned score per head whose exponential joins the softmax's denominator once, unscaled, with no
       key and no value;
     * `out_gate=True`: head h's output is multiplied by sigmoid(h . Wg^T)[h], one number per token and head, read from
-      the same rows as the projections.
+      the same rows as the projections;
+    * `qkv_bias=True` / `out_bias=True`: a bias on q, k and v, added in the joined product, and one on the output projection;
+    * `softcap` c > 0: score <- c tanh(score / c) on the scaled score, before the softmax.
 
     q, k, v and the gate's logits are ONE joined product with 32-bit sums; norm, rotation and the cache write are one
     kernel; scores, softmax and the sink are 32-bit.
@@ -290,10 +294,15 @@ class GatedSinkAttention(Mixer):
 
     def __init__(self, dim: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: Optional[int],
                  rotary: Optional[RotaryTable], names: Dict[str, str], window: int = 0, scale: Optional[float] = None,
-                 qk_norm: Optional[str] = None, qk_norm_eps: float = 1e-6, sink: bool = False, out_gate: bool = False):
+                 qk_norm: Optional[str] = None, qk_norm_eps: float = 1e-6, sink: bool = False, out_gate: bool = False,
+                 qkv_bias: bool = False, out_bias: bool = False, softcap: float = 0.0):
         super().__init__(names)
         if n_heads % n_kv_heads != 0:
             raise ValueError(f"{n_heads} query heads cannot share {n_kv_heads} key/value heads")
+        if softcap < 0:
+            raise ValueError(f"a cap on the scores must not be negative, got {softcap}")
+        self.qkv_bias, self.out_bias, self.softcap = bool(qkv_bias), bool(out_bias), float(softcap)
+        self.b_in = self.bo = None
         if qk_norm not in (None, "whole"):
             raise ValueError(f"qk_norm must be None or 'whole', got {qk_norm!r}")
         self.dim, self.H, self.KV, self.dk = dim, n_heads, n_kv_heads, head_dim
@@ -318,12 +327,22 @@ class GatedSinkAttention(Mixer):
             s["sink"] = TensorSpec((self.H,), BIAS)
         if self.out_gate:
             s["wg"] = TensorSpec((self.H, self.dim), MATRIX)
+        if self.qkv_bias:
+            s.update({"bq": TensorSpec((self.H * self.dk,), BIAS), "bk": TensorSpec((self.KV * self.dk,), BIAS),
+                      "bv": TensorSpec((self.KV * self.dv,), BIAS)})
+        if self.out_bias:
+            s["bo"] = TensorSpec((self.dim,), BIAS)
         return s
 
     def place(self, local, dtype, device):
         joined = [local["wq"], local["wk"], local["wv"]] + ([local["wg"]] if self.out_gate else [])
         self.w_in = to_device_matrix(torch.cat(joined, dim=0), dtype, device)
         self.wo = to_device_matrix(local["wo"], dtype, device)
+        if self.qkv_bias:                        # the gate's logits (further columns of the joined product) have none
+            b = [local[n].to(torch.float32) for n in ("bq", "bk", "bv")] + ([torch.zeros(self.H)] if self.out_gate else [])
+            self.b_in = torch.cat(b, dim=0).to(device).contiguous()
+        if self.out_bias:
+            self.bo = to_device_vector(local["bo"], dtype, device)
         if self.qk_norm:
             self.q_norm = to_device_vector(local["q_norm"], dtype, device)
             self.k_norm = to_device_vector(local["k_norm"], dtype, device)
@@ -341,7 +360,7 @@ class GatedSinkAttention(Mixer):
         T = h.shape[0]
         k_cache, v_cache, table = ctx.kv(cache_layer)
         proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
-        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        linear(ctx, h, self.w_in, proj, self._bias_in(), EPI_BIAS if self.qkv_bias else EPI_NONE)
         self._joined(proj)
         q = ctx.empty((T, self.H * self.dk))
         ops.qk_norm_rope_write(proj, self.off_k, self.off_v, self.q_norm, self.k_norm, self.qk_norm_eps, ctx.positions,
@@ -351,7 +370,22 @@ class GatedSinkAttention(Mixer):
         attn = ctx.empty((T, self.H * self.dv))
         gate = proj[:, self.off_g:self.off_g + self.H] if self.out_gate else None
         self.attend(ctx, q, k_cache, v_cache, table, attn, gate)
+        if self.out_bias:
+            if epilogue == EPI_RESIDUAL:
+                ops.add_row_vector(out, self.bo)
+                linear(ctx, attn, self.wo, out, None, EPI_RESIDUAL)
+            else:
+                linear(ctx, attn, self.wo, out, self.bo, EPI_BIAS)
+            return
         linear(ctx, attn, self.wo, out, None, epilogue)
+
+    def _bias_in(self):
+        """The joined product's bias, as long as its matrix (a part that joined further rows has none for them)."""
+        if not self.qkv_bias:
+            return None
+        if self.b_in.shape[0] != self.w_in.shape[0]:
+            self.b_in = torch.cat([self.b_in, self.b_in.new_zeros(self.w_in.shape[0] - self.b_in.shape[0])]).contiguous()
+        return self.b_in
 
     def forward(self, ctx, h, residual, cache_layer, write_cache=True):
         self._run(ctx, h, residual, cache_layer, write_cache, EPI_RESIDUAL)
@@ -360,7 +394,8 @@ class GatedSinkAttention(Mixer):
         self._run(ctx, h, out, cache_layer, write_cache, EPI_NONE)
 
     def attend(self, ctx, q, k_cache, v_cache, table, out, gate):
-        paged_attention(ctx, q, k_cache, v_cache, table, out, self.H, self.KV, self.dk, self.window, self.scale, self.sinks, gate)
+        paged_attention(ctx, q, k_cache, v_cache, table, out, self.H, self.KV, self.dk, self.window, self.scale, self.sinks, gate,
+                        softcap=self.softcap)
 
 
 class ChunkedTalkingAttention(Mixer):
@@ -475,15 +510,22 @@ class ChunkedTalkingAttention(Mixer):
 
 
 class ParallelMixers(Mixer):
-    """Two mixers side by side that read the same rows; the result is the mean of the two, each RMS-normed over the
-    model width first with a plain weight of its own: (rms_norm(left(h)) * left_out + rms_norm(right(h)) * right_out) / 2.
-    Each mixer keeps its own cache, so this part's `cache_spec()` is the pair of theirs and it is handed a pair of cache
-    layers. A block that adds the result to the stream through a norm can take the two results as they are
-    (`mix_pair`) and do the means in the kernel that adds."""
+    """Two mixers side by side that read the same rows. Each mixer keeps its own cache, so this part's `cache_spec()` is the
+    pair of theirs and it is handed a pair of cache layers. How the two results join is `combine`:
 
-    def __init__(self, dim: int, left: Mixer, right: Mixer, norm_eps: float, names: Dict[str, str]):
+    * "rms_mean" (the default): the mean of the two, each RMS-normed over the model width first with a plain weight of its
+      own: (rms_norm(left(h)) * left_out + rms_norm(right(h)) * right_out) / 2. A block that adds the result to the stream
+      through a norm can take the two results as they are (`mix_pair`) and do the means in the kernel that adds.
+    * "weighted": left_scale * left(h) + right_scale * right(h) with two constants (`scales`), no tensors of its own; it can
+      add into a stream (`forward`)."""
+
+    def __init__(self, dim: int, left: Mixer, right: Mixer, norm_eps: float = 0.0, names: Optional[Dict[str, str]] = None,
+                 combine: str = "rms_mean", scales=(1.0, 1.0)):
         super().__init__(names)
+        if combine not in ("rms_mean", "weighted"):
+            raise ValueError(f"ParallelMixers: combine must be 'rms_mean' or 'weighted', got {combine!r}")
         self.dim, self.left, self.right, self.eps = dim, left, right, float(norm_eps)
+        self.combine, self.scales = combine, (float(scales[0]), float(scales[1]))
         self.left_out = self.right_out = None
 
     def children(self):
@@ -494,6 +536,8 @@ class ParallelMixers(Mixer):
         return bool(getattr(self.left, "graph_safe", False) and getattr(self.right, "graph_safe", False))
 
     def local_specs(self):
+        if self.combine == "weighted":
+            return {}
         return {"left_out": TensorSpec((self.dim,), NORM), "right_out": TensorSpec((self.dim,), NORM)}
 
     def cache_spec(self):
@@ -511,7 +555,18 @@ class ParallelMixers(Mixer):
         a = ctx.empty(tuple(out.shape), torch.float32)
         b = ctx.empty(tuple(out.shape), torch.float32)
         self.mix_pair(ctx, h, a, b, cache_layers, write_cache)
+        if self.combine == "weighted":
+            out.zero_()
+            ops.add_scaled_pair(out, a, self.scales[0], b, self.scales[1])
+            return
         ops.pair_rms_mean(a, self.left_out, b, self.right_out, self.eps, out)
 
     def forward(self, ctx, h, residual, cache_layers, write_cache=True) -> None:
-        raise NotImplementedError("ParallelMixers writes its result (`mix`); blocks that add a mixer's result unchanged do not use it")
+        if self.combine != "weighted":
+            raise NotImplementedError("ParallelMixers with the normed mean writes its result (`mix`); blocks that add a mixer's result unchanged do not use it")
+        a = ctx.empty(tuple(residual.shape), torch.float32)
+        b = ctx.empty(tuple(residual.shape), torch.float32)
+        after, ctx.next_norm = ctx.next_norm, None       # the two results are not the stream: neither product may begin a norm
+        self.mix_pair(ctx, h, a, b, cache_layers, write_cache)
+        ctx.next_norm = after
+        ops.add_scaled_pair(residual, a, self.scales[0], b, self.scales[1])

@@ -64,6 +64,38 @@ class PreNormBlock(Part):
         return norm.forward(ctx, x)
 
 
+class ParallelBlock(Part):
+    """ONE norm in front of both sublayers, which read the same rows and whose results join the stream together:
+
+        h = norm(x);   x += mixer(h) + ffn(h)          (a block without a feed-forward has only the first)
+
+    Both sublayers add into the 32-bit stream in place (the rows h were made before either wrote)."""
+
+    def __init__(self, norm, mixer, ffn=None):
+        super().__init__()
+        self.mixer_norm, self.mixer, self.ffn = norm, mixer, ffn
+
+    def children(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn) if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    @property
+    def graph_safe(self) -> bool:
+        return bool(getattr(self.mixer, "graph_safe", False) and (self.ffn is None or getattr(self.ffn, "graph_safe", False)))
+
+    def forward(self, ctx, x, cache_layer, write_cache: bool = True) -> None:
+        h = self.mixer_norm.forward(ctx, x)
+        # only the sublayer that adds LAST leaves the finished row: it alone may begin the norm that reads the stream next
+        ctx.next_norm = None if self.ffn is not None else ctx.norm_after_block
+        self.mixer.forward(ctx, h, x, cache_layer, write_cache)
+        if self.ffn is not None:
+            ctx.next_norm = ctx.norm_after_block
+            self.ffn.forward(ctx, h, x)
+        ctx.next_norm = None
+
+
 class ResidualGate(Part):
     """The logits of a gate on a sublayer's result: h . W^T (+ b), one per channel of the stream, 32-bit. The sigmoid and
     the product with the sublayer's result belong to the kernel that adds the result to the stream."""

@@ -35,20 +35,31 @@ class FeedForward(Part):
 
 
 class DenseMLP(FeedForward):
-    """down(act(up(h))), no biases, no gate branch; `activation`: "gelu" (exact, erf), "gelu_tanh" or "silu",
-    evaluated in 32-bit on the up product's 32-bit sums."""
+    """down(act(up(h))), no biases, no gate branch; `activation`: "gelu" (exact, erf), "gelu_tanh", "silu" or "xielu",
+    evaluated in 32-bit on the up product's 32-bit sums. xIELU has two learned numbers p, q (a tensor `act` [2]):
+    z > 0: softplus(p) z^2 + z / 2; z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z / 2."""
     graph_safe = True
-    ACTIVATIONS = {"silu": ops.ACT_SILU, "gelu": ops.ACT_GELU_ERF, "gelu_tanh": ops.ACT_GELU_TANH}
+    ACTIVATIONS = {"silu": ops.ACT_SILU, "gelu": ops.ACT_GELU_ERF, "gelu_tanh": ops.ACT_GELU_TANH, "xielu": None}
 
     def __init__(self, dim: int, hidden: int, names: Dict[str, str], activation: str = "gelu"):
         super().__init__(names)
         if activation not in self.ACTIVATIONS:
             raise ValueError(f"DenseMLP: activation must be one of {sorted(self.ACTIVATIONS)}, got {activation!r}")
         self.dim, self.hidden, self.activation = dim, hidden, activation
-        self.w_up = self.w_down = None
+        self.w_up = self.w_down = self.act_args = None
 
     def local_specs(self):
-        return {"w_up": TensorSpec((self.hidden, self.dim), MATRIX), "w_down": TensorSpec((self.dim, self.hidden), MATRIX)}
+        s = {"w_up": TensorSpec((self.hidden, self.dim), MATRIX), "w_down": TensorSpec((self.dim, self.hidden), MATRIX)}
+        if self.activation == "xielu":
+            s["act"] = TensorSpec((2,), BIAS)
+        return s
+
+    def place(self, local, dtype, device):
+        self.w_up = to_device_matrix(local["w_up"], dtype, device)
+        self.w_down = to_device_matrix(local["w_down"], dtype, device)
+        if self.activation == "xielu":
+            p, q = (float(v) for v in local["act"].to(torch.float32))
+            self.act_args = ops.xielu_args(p, q, device)
 
     def join_rows(self, weight) -> None:
         """Further rows for the up product's matrix, from a part that reads the same rows (a gate on this feed-forward's
@@ -60,7 +71,13 @@ class DenseMLP(FeedForward):
 
     def _run(self, ctx, h, out, epilogue):
         act = ctx.empty((h.shape[0], self.hidden))
-        rest = ops.linear_act(h, self.w_up, act, self.ACTIVATIONS[self.activation], fast=ctx.fast)
+        if self.activation == "xielu":
+            sums = ctx.empty((h.shape[0], self.w_up.shape[0]), torch.float32)
+            linear(ctx, h, self.w_up, sums, None, EPI_NONE)
+            ops.xielu(sums, act, self.act_args)
+            rest = sums[:, self.hidden:] if self.w_up.shape[0] > self.hidden else None
+        else:
+            rest = ops.linear_act(h, self.w_up, act, self.ACTIVATIONS[self.activation], fast=ctx.fast)
         self.joined_out = rest[:, self.n_own - self.hidden:] if rest is not None else None
         linear(ctx, act, self.w_down, out, None, epilogue)
 
@@ -202,6 +219,35 @@ class SumFeedForward(FeedForward):
             p.forward(ctx, h, out)
 
 
+class RowGatedFeedForward(FeedForward):
+    """A feed-forward whose result is multiplied by sigmoid(w . h), ONE number per token (`gate` [1, dim]), before it joins
+    the stream: x += sigmoid(h gate^T) * inner(h). The gate's logit is 32-bit."""
+
+    def __init__(self, dim: int, inner: FeedForward, names: Dict[str, str]):
+        super().__init__(names)
+        self.dim, self.inner = dim, inner
+        self.gate = None
+
+    def children(self):
+        return (self.inner,)
+
+    @property
+    def graph_safe(self) -> bool:
+        return bool(getattr(self.inner, "graph_safe", False))
+
+    def local_specs(self):
+        return {"gate": TensorSpec((1, self.dim), MATRIX)}
+
+    def forward(self, ctx, h, residual):
+        after, ctx.next_norm = ctx.next_norm, None       # the inner result is not the stream: its product begins no norm
+        y = ctx.empty(tuple(residual.shape), torch.float32)
+        self.inner.apply(ctx, h, y)
+        ctx.next_norm = after
+        logit = ctx.empty((h.shape[0], 1), torch.float32)
+        linear(ctx, h, self.gate, logit, None, EPI_NONE)
+        ops.add_row_gated(residual, y, logit)
+
+
 class RoutedExperts(FeedForward):
     """A mixture of experts: `n_experts` small SwiGLU feed-forwards without biases, of which each token uses `top`.
 
@@ -211,21 +257,32 @@ class RoutedExperts(FeedForward):
     groups can be chosen. The result is the weighted sum of the chosen experts' outputs, added in the order of the choice.
     The experts' matrices are stacked ([E, 2 * hidden, dim] gate rows then up rows, [E, dim, hidden]); every (token,
     chosen expert) pair is a row of two products whose rows each use the matrix of their own expert. `activation` /
-    `limit`: the experts' gated activation, as in `GluMLP`, evaluated in the first product's epilogue."""
+    `limit`: the experts' gated activation, as in `GluMLP`, evaluated in the first product's epilogue.
+
+    Further choices: `score` "sigmoid" or "softmax" (the softmax of z over ALL router outputs); `group_score` "top2" (the sum
+    of a group's two largest choice scores) or "max" (its largest); `n_identity`: the router has `n_experts + n_identity`
+    outputs, and the last `n_identity` are identity experts without tensors whose output is the input row h itself (times
+    the weight); groups are formed over experts and identity experts together."""
     graph_safe = True
+    SCORES = {"sigmoid": ops.SCORE_SIGMOID, "softmax": ops.SCORE_SOFTMAX}
 
     def __init__(self, dim: int, hidden: int, n_experts: int, top: int, names: Dict[str, str], n_groups: int = 1,
-                 keep_groups: int = 1, correction: bool = True, activation: str = "silu", limit: float = 0.0):
+                 keep_groups: int = 1, correction: bool = True, activation: str = "silu", limit: float = 0.0,
+                 score: str = "sigmoid", group_score: str = "top2", n_identity: int = 0):
         super().__init__(names)
+        if score not in self.SCORES or group_score not in ("top2", "max") or n_identity < 0:
+            raise ValueError(f"RoutedExperts: score {score!r}, group_score {group_score!r}, {n_identity} identity experts")
+        self.score, self.group_top, self.n_identity = self.SCORES[score], 2 if group_score == "top2" else 1, int(n_identity)
+        self.n_out = n_experts + self.n_identity          # the router's outputs
         if activation not in GluMLP.KINDS:
             raise ValueError(f"experts: activation must be one of {sorted(GluMLP.KINDS)}, got {activation!r}")
         if activation == "clamped" and not limit > 0:
             raise ValueError(f"experts: the clamped activation needs a positive limit, got {limit}")
         self.activation, self.limit = activation, float(limit)
-        if n_experts % n_groups != 0 or not 1 <= keep_groups <= n_groups:
-            raise ValueError(f"RoutedExperts: {n_experts} experts in {n_groups} groups, {keep_groups} kept")
-        if not 1 <= top <= keep_groups * (n_experts // n_groups):
-            raise ValueError(f"RoutedExperts: {top} experts a token out of {keep_groups} groups of {n_experts // n_groups}")
+        if self.n_out % n_groups != 0 or not 1 <= keep_groups <= n_groups:
+            raise ValueError(f"RoutedExperts: {self.n_out} experts in {n_groups} groups, {keep_groups} kept")
+        if not 1 <= top <= keep_groups * (self.n_out // n_groups):
+            raise ValueError(f"RoutedExperts: {top} experts a token out of {keep_groups} groups of {self.n_out // n_groups}")
         self.dim, self.hidden, self.E, self.top = dim, hidden, n_experts, top
         self.n_groups, self.keep_groups, self.has_correction = n_groups, keep_groups, bool(correction)
         self.router = self.correction = self.w_gate_up = self.w_down = self.act_args = None
@@ -233,9 +290,9 @@ class RoutedExperts(FeedForward):
 
     def choice_specs(self):
         """The tensors that choose a token's experts."""
-        s = {"router": TensorSpec((self.E, self.dim), MATRIX)}
+        s = {"router": TensorSpec((self.n_out, self.dim), MATRIX)}
         if self.has_correction:
-            s["correction"] = TensorSpec((self.E,), BIAS)
+            s["correction"] = TensorSpec((self.n_out,), BIAS)
         return s
 
     def local_specs(self):
@@ -261,11 +318,11 @@ class RoutedExperts(FeedForward):
     def route(self, ctx, h):
         """(experts [T, top] int32, weights [T, top] 32-bit) of the rows h."""
         T = h.shape[0]
-        z = ctx.empty((T, self.E), torch.float32)
+        z = ctx.empty((T, self.n_out), torch.float32)
         linear(ctx, h, self.router, z, None, EPI_NONE)            # 32-bit sums of exact products (the rows may be bfloat16 roundings)
         ids = torch.empty((T, self.top), dtype=torch.int32, device=ctx.device)
         wts = ctx.empty((T, self.top), torch.float32)
-        ops.moe_route(z, self.correction, self.top, self.n_groups, self.keep_groups, ids, wts)
+        ops.moe_route(z, self.correction, self.top, self.n_groups, self.keep_groups, ids, wts, self.score, self.group_top)
         if self.record is not None:
             self.record.append(ids.clone())
         return ids, wts
@@ -282,13 +339,16 @@ class RoutedExperts(FeedForward):
             ops.gemm_grouped(rows, self.w_gate_up, tile_expert, act, EPI_SWIGLU, self.act_args)
             y = ctx.empty((row_src.numel(), self.dim), torch.float32)
             ops.gemm_grouped(act, self.w_down, tile_expert, y, EPI_NONE)
-            ops.moe_combine_rows(y, pos, wts, out, add=add)
+            ops.moe_combine_rows(y, pos, wts, out, add=add, x=h if self.n_identity else None)
             return
         act = ctx.empty((T * self.top, self.hidden))
         ops.expert_gemm_plain(h, self.top, self.w_gate_up, ids, act, EPI_SWIGLU, self.act_args)
         y = ctx.empty((T * self.top, self.dim), torch.float32)
         ops.expert_gemm_plain(act, 1, self.w_down, ids, y, EPI_NONE)
-        ops.moe_combine(y, wts, out, add=add)
+        if self.n_identity:
+            ops.moe_combine(y, wts, out, add=add, ids=ids, n_real=self.E, x=h)
+        else:
+            ops.moe_combine(y, wts, out, add=add)
 
     def forward(self, ctx, h, residual):
         self._run(ctx, h, residual, True)

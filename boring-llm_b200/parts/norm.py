@@ -7,20 +7,28 @@ import torch
 
 from ..kernels import ops
 from ..weights import TensorSpec, NORM, BIAS
-from .base import Part
+from .base import Part, to_device_vector
 
 
 class RMSNorm(Part):
     """y = x / sqrt(mean(x^2) + eps) * weight, statistics in 32-bit, the weight used as stored
-    (src/math.br:18-36). Input: the 32-bit residual stream; output: the engine's activation dtype."""
+    (src/math.br:18-36). Input: the 32-bit residual stream; output: the engine's activation dtype.
+    `scalar_weight`: the checkpoint holds ONE number (a tensor without dimensions) that multiplies every coordinate; it is
+    spread over the width when it is placed, so every kernel that takes an RMS norm's weight takes this one."""
 
-    def __init__(self, dim: int, eps: float, names: Dict[str, str]):
+    def __init__(self, dim: int, eps: float, names: Dict[str, str], scalar_weight: bool = False):
         super().__init__(names)
-        self.dim, self.eps = dim, float(eps)
+        self.dim, self.eps, self.scalar_weight = dim, float(eps), bool(scalar_weight)
         self.weight: Optional[torch.Tensor] = None
 
     def local_specs(self):
-        return {"weight": TensorSpec((self.dim,), NORM)}
+        return {"weight": TensorSpec(() if self.scalar_weight else (self.dim,), NORM)}
+
+    def place(self, local, dtype, device):
+        w = local["weight"]
+        if self.scalar_weight:
+            w = w.reshape(1).expand(self.dim).contiguous()
+        self.weight = to_device_vector(w, dtype, device)
 
     def forward(self, ctx, x: torch.Tensor, row_idx: Optional[torch.Tensor] = None, pending_ok: bool = False):
         """The normed rows. `pending_ok`: the caller can finish a norm that the product before it has begun; it then

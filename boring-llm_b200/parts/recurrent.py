@@ -339,3 +339,134 @@ class ShiftedDecayRecurrence(_StateMixer):
         y = ctx.empty((T, H * dk))
         ops.head_norm_gate_ext(o, self.norm, g, ops.GATE_SILU, self.eps, y, H, dk)
         linear(ctx, y, self.wo, out, None, epilogue)
+
+
+class Retention(_StateMixer):
+    """Linear attention with a FIXED decay per head and no softmax or denominator. With q = h Wq^T and k = h Wk^T (heads of
+    `key_dim`), both rotated by the token's position (any `RotaryTable` with pairs in halves; partial rotation), k then times
+    key_dim^(-1/2), and v = h Wv^T (heads of `value_dim`):
+
+        S_t = c_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t                (c_h: `decays`, one constant per head)
+
+    Each head's o is divided by its root mean square (no weight), the heads are joined, multiplied by silu(h Wg^T) and
+    projected by Wo. One joined product makes q | k | v | g with 32-bit sums; rotation, the key's factor and the decays are one
+    kernel in 32-bit; the scan is `GatedLinearAttention`'s. The slot holds S [H, key_dim, value_dim]."""
+    RULE = ops.RULE_GLA
+
+    def __init__(self, dim: int, n_heads: int, key_dim: int, value_dim: int, decays, rotary, norm_eps: float, names: Dict[str, str]):
+        super().__init__(names)
+        decays = [float(c) for c in decays]
+        if len(decays) != n_heads:
+            raise ValueError(f"Retention: {len(decays)} decays for {n_heads} heads")
+        if any(not 0.0 <= c <= 1.0 for c in decays):
+            raise ValueError(f"Retention: decays must lie in [0, 1], got {decays}")
+        if rotary is not None and rotary.pairs != "halves":
+            raise ValueError("Retention: the rotation pairs value i with i + n / 2")
+        self.dim, self.H, self.dk, self.dv = dim, n_heads, key_dim, value_dim
+        self.decays, self.rotary, self.eps = decays, rotary, float(norm_eps)
+        self.off_k, self.off_v = self.H * self.dk, 2 * self.H * self.dk
+        self.off_g = self.off_v + self.H * self.dv
+        self.w_in = self.wo = self.head_decay = self.no_freq = None
+
+    def local_specs(self):
+        H, dk, dv, d = self.H, self.dk, self.dv, self.dim
+        return {"wq": TensorSpec((H * dk, d), MATRIX), "wk": TensorSpec((H * dk, d), MATRIX), "wv": TensorSpec((H * dv, d), MATRIX),
+                "wg": TensorSpec((H * dv, d), MATRIX), "wo": TensorSpec((d, H * dv), MATRIX)}
+
+    def place(self, local, dtype, device):
+        self.w_in = to_device_matrix(torch.cat([local[n] for n in ("wq", "wk", "wv", "wg")], dim=0), dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        self.head_decay = torch.tensor(self.decays, dtype=torch.float32, device=device)
+        self.no_freq = torch.zeros(1, dtype=torch.float32, device=device)
+        if self.rotary is not None:
+            self.rotary.to(device)
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dv,), "float32")
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        self._check(write_cache)
+        T, H, dk, dv = h.shape[0], self.H, self.dk, self.dv
+        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
+        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        self._joined(proj)
+        rot = self.rotary
+        q, k, decay = ops.rope_decay_prep(proj, self.off_k, ctx.positions, rot.inv_freq if rot is not None else self.no_freq,
+                                          rot.rot_half if rot is not None else 0, self.head_decay, dk ** -0.5, H, dk)
+        o = ctx.empty((T, H * dv), torch.float32)
+        ops.recurrent_scan(ops.RULE_GLA, q, k, proj[:, self.off_v:self.off_g], decay, None, 1.0, ctx.state(cache_layer), ctx.slots,
+                           ctx.cu_q, o, H, H, dk, dv, parts=self._step_parts(ctx))
+        y = ctx.empty((T, H * dv))
+        ops.head_norm_gate(o, None, proj[:, self.off_g:self.off_g + H * dv], ops.GATE_SILU, self.eps, y, H, dv)
+        linear(ctx, y, self.wo, out, None, epilogue)
+
+
+class StateSpaceDuality(_StateMixer):
+    """A selective state-space mixer whose decay is one number per head and token (Mamba-2). With inner = heads * value_dim,
+    N = `state`, G = `groups`, the joined product W_in h is laid out [z: inner | x: inner | B: G N | C: G N | dt: heads]. x, B
+    and C pass a short causal convolution per channel (taps [channels, n], the last column the current token's, a bias per
+    channel, zeros before the start) and a SiLU; dt <- softplus(dt + dt_bias). Per head h (it reads B and C of group
+    h // (heads / G)):
+
+        S_t = exp(-exp(A_log_h) dt_t) S_(t-1) + dt_t B_t x_t^T   (S: N x value_dim),     y_t = S_t^T C_t + D_h x_t
+
+    then y (heads joined) is multiplied by silu(z) and after that RMS-normed in `norm_groups` equal parts of the row (each by
+    its own root mean square), times a weight, and projected by Wo. B is the scan's key, C its query, dt x its value: the
+    scan is `GatedLinearAttention`'s. The slot holds S [H, N, value_dim] and the convolution's last n - 1 inputs; dt, decays,
+    state, gate and norm are 32-bit."""
+    RULE = ops.RULE_GLA
+
+    def __init__(self, dim: int, n_heads: int, value_dim: int, state: int, groups: int, conv_taps: int, norm_groups: int,
+                 norm_eps: float, names: Dict[str, str]):
+        super().__init__(names)
+        if n_heads % groups != 0:
+            raise ValueError(f"StateSpaceDuality: {n_heads} heads cannot share {groups} groups of B and C")
+        inner = n_heads * value_dim
+        if norm_groups < 1 or inner % norm_groups != 0:
+            raise ValueError(f"StateSpaceDuality: {inner} inner channels do not split into {norm_groups} equal parts")
+        self.dim, self.H, self.dk, self.dv, self.G = dim, n_heads, state, value_dim, groups
+        self.taps, self.norm_groups, self.eps = int(conv_taps), int(norm_groups), float(norm_eps)
+        self.inner = inner
+        self.C = inner + 2 * groups * state              # channels that pass the convolution: x | B | C
+        self.off_dt = inner + self.C
+        self.n_in = self.off_dt + n_heads
+        self.w_in = self.wo = self.conv = self.conv_bias = self.dt_bias = self.rate = self.skip = self.norm = None
+
+    def local_specs(self):
+        H, d = self.H, self.dim
+        return {"w_in": TensorSpec((self.n_in, d), MATRIX), "conv": TensorSpec((self.C, self.taps), MATRIX),
+                "conv_bias": TensorSpec((self.C,), BIAS), "dt_bias": TensorSpec((H,), BIAS), "a_log": TensorSpec((H,), BIAS),
+                "skip": TensorSpec((H,), BIAS), "norm": TensorSpec((self.inner,), NORM), "wo": TensorSpec((d, self.inner), MATRIX)}
+
+    def place(self, local, dtype, device):
+        self.w_in = to_device_matrix(local["w_in"], dtype, device)
+        self.wo = to_device_matrix(local["wo"], dtype, device)
+        f32 = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
+        self.conv, self.conv_bias = f32(local["conv"]), f32(local["conv_bias"])
+        self.dt_bias, self.skip = f32(local["dt_bias"]), f32(local["skip"])
+        self.rate = torch.exp(local["a_log"].to(torch.float32)).to(device).contiguous()
+        self.norm = to_device_vector(local["norm"], dtype, device)
+
+    def cache_spec(self):
+        return StateSpec((self.H * self.dk * self.dv + (self.taps - 1) * self.C,), "float32")
+
+    def _run(self, ctx, h, out, cache_layer, write_cache, epilogue):
+        self._check(write_cache)
+        T, H, G, N, dv, inner, C = h.shape[0], self.H, self.G, self.dk, self.dv, self.inner, self.C
+        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
+        linear(ctx, h, self.w_in, proj, None, EPI_NONE)
+        self._joined(proj)
+        state = ctx.state(cache_layer)
+        tail = state[:, H * N * dv:]
+        xbc_in = proj[:, inner:inner + C]
+        xbc = ctx.empty((T, C), torch.float32)
+        ops.conv_silu_unit(xbc_in, self.conv, tail, ctx.slots, ctx.tok_req, ctx.cu_q, xbc, 0, 0, 1, 1.0, 0.0, bias=self.conv_bias)
+        ops.conv_tail_update(xbc_in, self.taps, tail, ctx.slots, ctx.cu_q, C)
+        x = xbc[:, :inner]
+        decay, v = ops.ssd_prep(proj[:, self.off_dt:self.off_dt + H], self.dt_bias, self.rate, x, H, N, dv)
+        o = ctx.empty((T, inner), torch.float32)
+        ops.recurrent_scan(ops.RULE_GLA, xbc[:, inner + G * N:], xbc[:, inner:inner + G * N], v, decay, None, 1.0, state, ctx.slots,
+                           ctx.cu_q, o, H, G, N, dv, parts=self._step_parts(ctx))
+        y = ctx.empty((T, inner))
+        ops.gated_group_norm(o, x, self.skip, dv, proj[:, :inner], self.norm, self.norm_groups, self.eps, y)
+        linear(ctx, y, self.wo, out, None, epilogue)
