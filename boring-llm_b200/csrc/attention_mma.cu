@@ -38,6 +38,7 @@ struct AttnParams {
     float* part_o; float* part_ml; int n_splits;
     int* counters;                // decode with slices: one per (request, head group), zero between launches
     int H, KV, window; float scale_log2;
+    float cap_log2;               // > 0: a cap c on the scaled scores, s <- c tanh(s / c), here times log2 e (0: none)
     BlAttnTail tail;              // a sink per head and a gate per (token, head), or nulls
     // Options of attention whose heads are mixed after the softmax (all zero / null: plain attention).
     int chunk;                    // > 0: position i sees only keys from i - i % chunk on
@@ -186,7 +187,7 @@ template <int DH, int NT, int KROWS = KB>
 __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff, int key_abs0,
                                            const unsigned (&qf)[DH / 16][4], float (&o)[DH / 8][4],
                                            float (&m)[2], float (&l)[2], const int (&pos)[2], const int (&lo_row)[2],
-                                           const float (&scale_log2)[2]) {
+                                           const float (&scale_log2)[2], float cap_log2 = 0.f) {
     constexpr int ROW = Tiles<DH>::ROW;
     const __nv_bfloat16* ks = stage;
     const __nv_bfloat16* vs = stage + KROWS * ROW;
@@ -203,6 +204,22 @@ __device__ __forceinline__ void block_step(const __nv_bfloat16* stage, int koff,
             ldmatrix_x4(b, ks + (koff + np * 16 + (mi >> 1) * 8 + ri) * ROW + kk * 16 + (mi & 1) * 8);
             mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
             mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    if (cap_log2 > 0.f) {
+        // a cap on the scores: raw score r becomes tanh(r a) / a with a = scale / cap, so that the scaled score is
+        // cap tanh(r scale / cap); monotonic, so the maximum of the raw scores still gives the scaled maximum. Before the
+        // mask: tanh(-inf) is finite. tanh(x) = 1 - 2 / (1 + 2^(2 x log2 e)).
+        float a[2], ia[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) { a[h] = scale_log2[h] / cap_log2; ia[h] = cap_log2 / scale_log2[h]; }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float x = s[n][c] * a[c >> 1];
+                s[n][c] = (1.0f - __fdividef(2.0f, 1.0f + bl_ex2(x * 2.8853900817779268f))) * ia[c >> 1];
+            }
         }
     }
     // mask, running maximum. The maximum is taken over the raw scores (the scale is positive) and scaled once;
@@ -410,7 +427,7 @@ attention_mma_kernel(const AttnParams p) {
             else if (pending == 1) cp_async_wait<1>(); else cp_async_wait<0>();
             __syncwarp();
             __nv_bfloat16* st = wring + (i % WSTAGES) * WSTAGE;
-            block_step<DH, 2, PAGE>(st, 0, (b_begin + i) * KB + warp * PAGE, qf, o, m, l, pos, lo_row, sc_row);
+            block_step<DH, 2, PAGE>(st, 0, (b_begin + i) * KB + warp * PAGE, qf, o, m, l, pos, lo_row, sc_row, p.cap_log2);
             __syncwarp();
             if (issued < nb) {                        // the stage just used takes the page WSTAGES blocks on
                 load_page<DH>(st, p, table, kvh, vh, (b_begin + issued) * KB + warp * PAGE, lo, hi);
@@ -428,7 +445,7 @@ attention_mma_kernel(const AttnParams p) {
             const int b = b_begin + i, st = i & 1;
             if (issued - (i + 1) >= 1) cp_async_wait<1>(); else cp_async_wait<0>();   // block i has landed
             __syncthreads();
-            block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, lo_row, sc_row);
+            block_step<DH, 8>(smem + st * STAGE, 0, b * KB, qf, o, m, l, pos, lo_row, sc_row, p.cap_log2);
             __syncthreads();
             if (issued < nb) {                        // the stage just used takes the block after next
                 load_block<DH>(smem + st * STAGE, p, table, kvh, vh, (b_begin + issued) * KB, lo, hi);
@@ -747,13 +764,25 @@ extern "C" int bl_attention_prefill_tail(const void* q, const void* k_cache, con
                                          int n_tiles, void* out, int H, int KV, int dh, int page_size, int window,
                                          float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate,
                                          void* stream) {
+    return bl_attention_prefill_cap(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, tiles, n_tiles, out, H, KV, dh,
+                                    page_size, window, scale, sinks, sink_dtype, gate, ld_gate, 0.f, stream);
+}
+
+// ... and a cap c > 0 on the scaled scores, s <- c tanh(s / c), before the softmax (0: none).
+extern "C" int bl_attention_prefill_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                        const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
+                                        int n_tiles, void* out, int H, int KV, int dh, int page_size, int window,
+                                        float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate,
+                                        float softcap, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (!(softcap >= 0.f)) BL_FAIL("bl_attention_prefill: a cap on the scores must not be negative, got %g", (double)softcap);
     if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
     AttnParams p = {};
     p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)k_cache; p.vc = (const __nv_bfloat16*)v_cache;
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.work = tiles; p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr; p.n_splits = 1; p.H = H; p.KV = KV; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.cap_log2 = softcap * 1.4426950408889634f;
     p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
     if ((long long)n_tiles * H > 2147483647LL) BL_FAIL("bl_attention_prefill: %d tiles x %d heads are more blocks than a launch takes", n_tiles, H);
     return dispatch<false>(dh, p, dim3(n_tiles * H, 1, 1), (cudaStream_t)stream);
@@ -778,7 +807,17 @@ extern "C" int bl_attention_decode_tail(const void* q, const void* k_cache, cons
                                         int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh,
                                         int page_size, int window, float scale, const void* sinks, int sink_dtype,
                                         const float* gate, int ld_gate, void* stream) {
+    return bl_attention_decode_cap(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, reqs, n, n_splits, scratch, counters,
+                                   out, H, KV, dh, page_size, window, scale, sinks, sink_dtype, gate, ld_gate, 0.f, stream);
+}
+
+extern "C" int bl_attention_decode_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                       const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                       int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh,
+                                       int page_size, int window, float scale, const void* sinks, int sink_dtype,
+                                       const float* gate, int ld_gate, float softcap, void* stream) {
     if (n <= 0) return 0;
+    if (!(softcap >= 0.f)) BL_FAIL("bl_attention_decode: a cap on the scores must not be negative, got %g", (double)softcap);
     if (check(H, KV, dh, page_size, max_pages, window, scale)) return 1;
     if (n_splits < 1 || n_splits > 256) BL_FAIL("bl_attention_decode: %d slices (1..256)", n_splits);
     if (n_splits > 1 && scratch != nullptr && counters == nullptr)
@@ -792,6 +831,7 @@ extern "C" int bl_attention_decode_tail(const void* q, const void* k_cache, cons
     p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n * H * n_splits * dh : nullptr;
     p.counters = counters;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.cap_log2 = softcap * 1.4426950408889634f;
     p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
     const int G = H / KV;
     return dispatch<true>(dh, p, dim3(n_splits, KV * ((G + 15) / 16), n), (cudaStream_t)stream);

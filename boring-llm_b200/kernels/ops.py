@@ -348,16 +348,21 @@ def attention_mma_supported(dtype: torch.dtype, dh: int, page_size: int) -> bool
 
 
 def attention_prefill(q, k_cache, v_cache, cu_q, ctx_len, block_table, tiles, out, H: int, window: int,
-                      scale: float, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                      scale: float, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                      softcap: float = 0.0) -> None:
     """Tensor-core attention for requests with several new tokens. tiles: int32 [n, 2] = (request, first token
-    of a 64-token tile among the request's new tokens)."""
+    of a 64-token tile among the request's new tokens). `softcap` c > 0: scaled scores pass c tanh(s / c)."""
     T = q.shape[0]
     _, KV, page_size, dh = k_cache.shape
     _need(q, "q", torch.bfloat16, (T, H * dh)); _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape); _need(out, "out", torch.bfloat16, (T, H * dh))
     _need(cu_q, "cu_q", torch.int32); _need(ctx_len, "ctx_len", torch.int32); _need(block_table, "block_table", torch.int32)
     _need(tiles, "tiles", torch.int32)
-    if sinks is None and gate is None:
+    if softcap > 0:
+        _call(_lib().bl_attention_prefill_cap, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), H, KV, dh, page_size, window,
+          ctypes.c_float(scale), *_tail(T, H, sinks, gate), ctypes.c_float(softcap), _stream())
+    elif sinks is None and gate is None:
         _call(_lib().bl_attention_prefill, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(tiles), tiles.shape[0], _p(out), H, KV, dh, page_size, window,
           ctypes.c_float(scale), _stream())
@@ -396,7 +401,7 @@ DECODE_CLUSTER_SPLITS = 16     # up to this many slices merge through distribute
 
 def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, out, H: int, window: int,
                      scale: float, scratch: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                     gate: Optional[torch.Tensor] = None) -> None:
+                     gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Tensor-core attention for requests with one new token; `reqs` int32 [n] lists them. The keys of each are
     cut into `n_splits` slices. Up to `DECODE_CLUSTER_SPLITS` slices without `scratch`: the slices of a request are
     the blocks of a cluster and merge in shared memory. More slices, or a `scratch` tensor (float32,
@@ -426,7 +431,11 @@ def attention_decode(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_sp
                 raise KernelError("attention_decode: its counters must exist before a capture (run the step once first)")
             # zero once; every launch leaves them at zero again
             counters = _decode_counters[q.device] = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=q.device)
-    if sinks is None and gate is None:
+    if softcap > 0:
+        _call(_lib().bl_attention_decode_cap, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(counters), _p(out), H, KV, dh,
+          page_size, window, ctypes.c_float(scale), *_tail(T, H, sinks, gate), ctypes.c_float(softcap), _stream())
+    elif sinks is None and gate is None:
         _call(_lib().bl_attention_decode, _p(q), _p(k_cache), _p(v_cache), _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(reqs), n, n_splits, _p(scratch if need else None), _p(counters), _p(out), H, KV, dh,
           page_size, window, ctypes.c_float(scale), _stream())

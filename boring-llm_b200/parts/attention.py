@@ -74,9 +74,9 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
     Otherwise, and always in float32, the plain kernel. Which requests those are comes from the step's plan
     (`attention_plan`). `sinks` [H] and `gate` (32-bit logits [T, >= H]) are what may follow the softmax: a score per
     head that joins the denominator, a sigmoid per (token, head) on the output. `softcap` c > 0: scaled scores pass
-    c tanh(s / c) before the softmax (the plain kernel has it)."""
+    c tanh(s / c) before the softmax (the plain and the `mma.sync` kernels have it)."""
     dv = v_cache.shape[3]
-    if not (ctx.fast and dv == dh and softcap == 0.0 and ops.attention_mma_supported(q.dtype, dh, k_cache.shape[2])):
+    if not (ctx.fast and dv == dh and ops.attention_mma_supported(q.dtype, dh, k_cache.shape[2])):
         ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, H, window, scale, sinks, gate,
                             softcap=softcap)
         return
@@ -87,10 +87,11 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
         ctx.plans[PLAN_KEY] = plan
     tiles64, tiles128, singles = plan.arrays["tiles64"], plan.arrays["tiles128"], plan.arrays["singles"]
     if tiles64.shape[0]:
-        if tiles128.shape[0] and ops.attention_prefill_tc_supported(q.dtype, dh, k_cache.shape[2]):
+        if tiles128.shape[0] and softcap == 0.0 and ops.attention_prefill_tc_supported(q.dtype, dh, k_cache.shape[2]):
             ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles128, out, H, window, scale, sinks, gate)
         else:
-            ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles64, out, H, window, scale, sinks, gate)
+            ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles64, out, H, window, scale, sinks, gate,
+                                  softcap=softcap)
     n = singles.shape[0]
     if n:
         # as many slices of the keys as fill the device once (the kernel knows how many of its blocks fit)
@@ -98,7 +99,7 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
         if window > 0:
             longest = min(longest, window + 64)
         G = H // KV
-        if ops.attention_decode_tma_supported(q.dtype, dh, k_cache.shape[2]):
+        if softcap == 0.0 and ops.attention_decode_tma_supported(q.dtype, dh, k_cache.shape[2]):
             # head sizes 64 and 128: the TMA-fed kernel, which knows how many slices pay for this many requests
             n_splits = ops.attention_decode_tma_splits(n, KV, G, dh, longest)
             ops.attention_decode_tma(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out, H, window, scale,
@@ -108,7 +109,7 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
         resident = ops.attention_decode_resident_blocks(dh)
         n_splits = max(1, min(-(-longest // 64), resident // (n * groups), DECODE_MAX_SPLITS))
         ops.attention_decode(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out, H, window, scale,
-                             sinks=sinks, gate=gate)
+                             sinks=sinks, gate=gate, softcap=softcap)
 
 
 class Mixer(Part):

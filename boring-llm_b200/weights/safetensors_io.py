@@ -127,7 +127,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dic
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store dtype {t.dtype} (tensor {name!r})")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""      # (a tensor without dimensions has one element)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)

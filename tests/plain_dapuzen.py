@@ -216,9 +216,10 @@ def routed_experts(h, w, c, forced=None, info=None):
     z = h @ w["router"].T
     s = torch.softmax(z, dim=-1)
     corr = w["correction"] if "correction" in w else torch.zeros(E + n_id, dtype=F64)
-    ids = choose_experts(s, corr, top, g.get("count", 1), g.get("keep", 1)) if forced is None else forced.to(torch.int64)
+    own = choose_experts(s, corr, top, g.get("count", 1), g.get("keep", 1))
+    ids = own if forced is None else forced.to(torch.int64)
     if info is not None:
-        info.append({"scores": s, "choice": s + corr, "ids": ids})
+        info.append({"scores": s, "choice": s + corr, "own": own, "groups": g.get("count", 1)})
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in ids[t].tolist():
