@@ -8,6 +8,7 @@ its roofline.
     python bench.py --design fezopel [--sizes 0.5b|3b] [--layers L]     # another design beside Qwen2 at equal sizes (its own JSON line)
     python bench.py --design kavotar [--sizes 0.5b|3b] [--layers L]     # the Kavotar design beside Fezopel and Qwen2 at equal sizes
     python bench.py --design miforax [--sizes 0.5b|3b] [--layers L]     # the Miforax design beside Fezopel and Qwen2 at equal sizes
+    python bench.py --design dapuzen [--sizes 0.5b|3b] [--layers L]     # the Dapuzen design beside Fezopel and Qwen2 at equal sizes
 
 One JSON line on standard output. A "step" is one decode step of the whole batch. Requests are real ones: random
 prompts admitted by the scheduler, prefilled in portions through the engine, then decoded; the model comes from the
@@ -421,6 +422,44 @@ def miforax_config(sizes, n_layers):
                                       "embedding": {"scale": 1.0}, "layers": layers, "max_position_embeddings": 32768})
 
 
+DAPUZEN_WINDOW = 1024
+DAPUZEN_PATTERN = ("parallel", "retention", "attention", "attention")     # repeated over the layers; the odd ones have experts
+DAPUZEN_EXPERTS, DAPUZEN_TOP, DAPUZEN_IDENTITY, DAPUZEN_GROUPS, DAPUZEN_KEEP = 14, 4, 2, 2, 1
+DAPUZEN_STATE = 128
+
+
+def dapuzen_config(sizes, n_layers):
+    """A Dapuzen model with the width, heads, head size, layers and vocabulary of a Qwen2.5 size: the attention mixers have
+    the Qwen2 heads and windows of 1,024 (the parallel layer's with capped scores and biases, beside a state-space mixer of
+    width / head size heads over a state of 128 in two groups); retention has half the heads with values twice as wide;
+    every second layer has the dense feed-forward with xIELU, the others 14 experts of a quarter of its hidden size and 2
+    identity experts, 4 a token from the better of 2 groups, beside a gated shared expert of half of it."""
+    import boring_llm_b200 as b
+    s = SIZES[sizes]
+    d, H, KV, dh, F, V = (s[k] for k in ("hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                                         "intermediate_size", "vocab_size"))
+    Hr = H // 2
+    att = {"heads": H, "kv_heads": KV, "dim": dh, "vdim": dh, "scale": dh ** -0.5, "mask": {"size": DAPUZEN_WINDOW},
+           "rot": {"base": 1000000.0, "dims": dh}}
+    left = {k: v for k, v in att.items() if k != "rot"}
+    left["softcap"] = 30.0
+    mixers = {
+        "attention": att,
+        "retention": {"heads": Hr, "dim": dh, "vdim": 2 * dh, "decay": [1.0 - 2.0 ** (-5 - 3 * i / max(1, Hr - 1)) for i in range(Hr)],
+                      "rot": {"base": 1000000.0, "dims": dh}},
+        "parallel": {"left": left, "right": {"heads": d // dh, "vdim": dh, "state": DAPUZEN_STATE, "groups": 2, "conv": 4, "norm_groups": 2},
+                     "left_scale": 0.8, "right_scale": 0.5},
+    }
+    moe = {"kind": "moe", "expert": {"ff": F // 4 // 8 * 8},
+           "router": {"experts": DAPUZEN_EXPERTS, "top": DAPUZEN_TOP, "identity": DAPUZEN_IDENTITY,
+                      "groups": {"count": DAPUZEN_GROUPS, "keep": DAPUZEN_KEEP}},
+           "shared": {"ff": F // 2 // 8 * 8}}
+    layers = [{"type": t, "mixer": mixers[t], "mlp": moe if i % 2 else {"kind": "dense", "ff": F}}
+              for i, t in ((i, DAPUZEN_PATTERN[i % len(DAPUZEN_PATTERN)]) for i in range(n_layers))]
+    return b.DapuzenConfig.from_dict({"architecture": "Dapuzen", "vocab": V, "width": d, "norm": {"eps": 1e-6},
+                                      "embedding": {"scale": 1.0}, "layers": layers, "max_position_embeddings": 32768})
+
+
 def kernel_time_line(eng, entries, again):
     """The time of every kernel of one step INSIDE its captured graph: the step is captured with a time stamp between
     every two kernels, then `again` (the same shape: it replays that graph) runs, and the stamps of the replay give
@@ -463,7 +502,7 @@ def design_bench(args):
     from boring_llm_b200.engine.runner import StepEntry
     pk = peaks()
     n_layers = args.layers or 8
-    makers = {"fezopel": fezopel_config, "kavotar": kavotar_config, "miforax": miforax_config,
+    makers = {"fezopel": fezopel_config, "kavotar": kavotar_config, "miforax": miforax_config, "dapuzen": dapuzen_config,
               "qwen2": lambda sizes, n: b.Qwen2Config.from_dict({**COMMON, **SIZES[sizes], "num_hidden_layers": n})}
     names = ("fezopel", "qwen2") if args.design == "fezopel" else (args.design, "fezopel", "qwen2")
     out = {"design": args.design, "beside": list(names[1:]), "sizes": args.sizes, "layers": n_layers, "dtype": "bf16", "data": "synthetic",
@@ -472,6 +511,9 @@ def design_bench(args):
         out.update(beside="qwen2", pattern=list(FEZOPEL_PATTERN), window=FEZOPEL_WINDOW)
     elif args.design == "miforax":
         out.update(window=MIFORAX_WINDOW, experts=[MIFORAX_EXPERTS, MIFORAX_TOP], latent=list(MIFORAX_LATENT[args.sizes]))
+    elif args.design == "dapuzen":
+        out.update(pattern=list(DAPUZEN_PATTERN), window=DAPUZEN_WINDOW, state=DAPUZEN_STATE,
+                   experts=[DAPUZEN_EXPERTS, DAPUZEN_TOP, DAPUZEN_IDENTITY, DAPUZEN_GROUPS, DAPUZEN_KEEP])
     else:
         out.update(pattern=list(KAVOTAR_PATTERN), chunk=KAVOTAR_CHUNK, experts=[KAVOTAR_EXPERTS, KAVOTAR_TOP, KAVOTAR_GROUPS, KAVOTAR_KEEP])
     clocks = ClockSampler()
@@ -537,7 +579,7 @@ def main():
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "prefill4", "mixed"],
                     help="run one part only and print its figures (for profilers; not the benchmark line)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--design", default="", choices=["", "fezopel", "kavotar", "miforax"],
+    ap.add_argument("--design", default="", choices=["", "fezopel", "kavotar", "miforax", "dapuzen"],
                     help="measure another design beside Qwen2 at equal sizes instead of the default workload (its own JSON line)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -403,6 +403,27 @@ __global__ void xielu_kernel(const float* x, TO* y, size_t count, int cols, size
     }
 }
 
+// The same, four values a thread: cols and both row strides multiples of 4, 16-byte aligned rows.
+template <typename TO>
+__global__ void xielu4_kernel(const float* x, TO* y, size_t count4, int cols4, size_t ld_x, size_t ld_y, const float* __restrict__ args) {
+    bl_pdl_trigger();
+    const float ap = args[0], an = args[1];
+    bl_pdl_wait();
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count4; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / cols4, c = (e % cols4) * 4;
+        const float4 a = *reinterpret_cast<const float4*>(x + r * ld_x + c);
+        const float o0 = bl_xielu(a.x, ap, an), o1 = bl_xielu(a.y, ap, an), o2 = bl_xielu(a.z, ap, an), o3 = bl_xielu(a.w, ap, an);
+        if constexpr (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(y + r * ld_y + c) = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(y + r * ld_y + c) = pk;
+        }
+    }
+}
+
 int grid_for(size_t count, int threads) {
     size_t b = (count + threads - 1) / threads;
     return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -563,6 +584,15 @@ extern "C" int bl_xielu(const float* x, long long ld_x, void* y, int y_dtype, lo
     if (count <= 0) return 0;
     if (ld_x < cols || ld_y < cols || !args) BL_FAIL("bl_xielu: rows of %d values are %lld and %lld apart", cols, ld_x, ld_y);
     cudaStream_t s = (cudaStream_t)stream;
+    if (y_dtype != BL_F32 && y_dtype != BL_BF16) BL_FAIL("bl_xielu: unknown dtype %d", y_dtype);
+    if (cols % 4 == 0 && ld_x % 4 == 0 && ld_y % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & (y_dtype == BL_F32 ? 15 : 7)) == 0) {
+        const size_t count4 = (size_t)count / 4;
+        const int g4 = grid_for(count4, 256);
+        if (y_dtype == BL_F32) BL_CUDA(bl_launch_dependent(xielu4_kernel<float>, dim3(g4), dim3(256), 0, s, x, (float*)y, count4, cols / 4, (size_t)ld_x, (size_t)ld_y, args));
+        else BL_CUDA(bl_launch_dependent(xielu4_kernel<__nv_bfloat16>, dim3(g4), dim3(256), 0, s, x, (__nv_bfloat16*)y, count4, cols / 4, (size_t)ld_x, (size_t)ld_y, args));
+        BL_CHECK_LAUNCH("bl_xielu");
+        return 0;
+    }
     const int g = grid_for((size_t)count, 256);
     if (y_dtype == BL_F32) BL_CUDA(bl_launch_dependent(xielu_kernel<float>, dim3(g), dim3(256), 0, s, x, (float*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, args));
     else if (y_dtype == BL_BF16) BL_CUDA(bl_launch_dependent(xielu_kernel<__nv_bfloat16>, dim3(g), dim3(256), 0, s, x, (__nv_bfloat16*)y, (size_t)count, cols, (size_t)ld_x, (size_t)ld_y, args));

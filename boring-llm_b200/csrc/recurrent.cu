@@ -717,19 +717,20 @@ ssd_prep_kernel(const float* raw, int ld_raw, const void* __restrict__ dt_bias, 
 }
 
 // Behind such a recurrence: u = (o + skip[h] * x) * silu(z) (the gate comes BEFORE the norm), then an RMS norm over each of
-// n_parts equal parts of the row (each part by its own root mean square), times w. One warp per (token, part); a part may
-// span several heads or a fraction of one. skip and x may be null (no skip term), z may be null (no gate).
+// n_parts equal parts of the row (each part by its own root mean square), times w. One block per (token, part); a part may
+// span several heads or a fraction of one. skip and x may be null (no skip term), z may be null (no gate). A thread keeps
+// up to GN_KEEP of its values between the two passes (parts of up to GN_KEEP * 128 values are read once); the sum of squares
+// is added in a fixed order (lanes, then warps).
+constexpr int GN_KEEP = 16;
 template <typename TY>
 __global__ void __launch_bounds__(WARPS * 32)
 gated_group_norm_kernel(const float* o, const float* x, int ld_x, const void* __restrict__ skip, int skip_dtype, int dv,
-                        const float* z, int ld_z, const void* __restrict__ w, int w_dtype, TY* __restrict__ y, int items, int n_parts,
+                        const float* z, int ld_z, const void* __restrict__ w, int w_dtype, TY* __restrict__ y, int n_parts,
                         int width, float eps) {
     bl_pdl_trigger();
     bl_pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int item = blockIdx.x * WARPS + (threadIdx.x >> 5);
-    if (item >= items) return;
-    const int t = item / n_parts, part = item % n_parts;
+    __shared__ float warp_ss[WARPS];
+    const int t = blockIdx.x / n_parts, part = blockIdx.x % n_parts;
     const int per = width / n_parts, c0 = part * per;
     auto value = [&](int c) {
         float u = o[(size_t)t * width + c];
@@ -737,10 +738,28 @@ gated_group_norm_kernel(const float* o, const float* x, int ld_x, const void* __
         if (z) u *= bl_silu(z[(size_t)t * ld_z + c]);
         return u;
     };
+    float keep[GN_KEEP];
     float ss = 0.f;
-    for (int i = lane; i < per; i += 32) { const float u = value(c0 + i); ss += u * u; }
-    const float inv = 1.0f / sqrtf(bl_warp_sum(ss) / (float)per + eps);
-    for (int i = lane; i < per; i += 32)
+#pragma unroll
+    for (int j = 0; j < GN_KEEP; ++j) {
+        const int i = threadIdx.x + j * WARPS * 32;
+        keep[j] = i < per ? value(c0 + i) : 0.f;
+        ss += keep[j] * keep[j];
+    }
+    for (int i = threadIdx.x + GN_KEEP * WARPS * 32; i < per; i += WARPS * 32) { const float u = value(c0 + i); ss += u * u; }
+    ss = bl_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < WARPS; ++k) total += warp_ss[k];
+    const float inv = 1.0f / sqrtf(total / (float)per + eps);
+#pragma unroll
+    for (int j = 0; j < GN_KEEP; ++j) {
+        const int i = threadIdx.x + j * WARPS * 32;
+        if (i < per) bl_store(y + (size_t)t * width + c0 + i, keep[j] * inv * (w ? bl_load_any(w, w_dtype, c0 + i) : 1.f));
+    }
+    for (int i = threadIdx.x + GN_KEEP * WARPS * 32; i < per; i += WARPS * 32)
         bl_store(y + (size_t)t * width + c0 + i, value(c0 + i) * inv * (w ? bl_load_any(w, w_dtype, c0 + i) : 1.f));
 }
 
@@ -988,14 +1007,15 @@ extern "C" int bl_gated_group_norm(const float* o, const float* x, int ld_x, con
     if (width <= 0 || n_parts <= 0 || width % n_parts != 0 || (x && (dv <= 0 || width % dv != 0 || ld_x < width || !skip)) ||
         (z && ld_z < width))
         BL_FAIL("bl_gated_group_norm: bad sizes width=%d parts=%d dv=%d ld_x=%d ld_z=%d", width, n_parts, dv, ld_x, ld_z);
-    const int items = T * n_parts, blocks = (items + WARPS - 1) / WARPS;
+    if ((long long)T * n_parts > 2147483647LL) BL_FAIL("bl_gated_group_norm: %d rows in %d parts are more blocks than a launch takes", T, n_parts);
+    const int blocks = T * n_parts;
     cudaStream_t s = (cudaStream_t)stream;
     if (y_dtype == BL_F32)
         BL_CUDA(bl_launch_dependent(gated_group_norm_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, s, o, x, ld_x, skip, skip_dtype, dv, z,
-                                    ld_z, w, w_dtype, (float*)y, items, n_parts, width, eps));
+                                    ld_z, w, w_dtype, (float*)y, n_parts, width, eps));
     else if (y_dtype == BL_BF16)
         BL_CUDA(bl_launch_dependent(gated_group_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, s, o, x, ld_x, skip, skip_dtype,
-                                    dv, z, ld_z, w, w_dtype, (__nv_bfloat16*)y, items, n_parts, width, eps));
+                                    dv, z, ld_z, w, w_dtype, (__nv_bfloat16*)y, n_parts, width, eps));
     else
         BL_FAIL("bl_gated_group_norm: unknown output dtype %d", y_dtype);
     BL_CHECK_LAUNCH("bl_gated_group_norm");
