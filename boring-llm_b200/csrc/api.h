@@ -200,11 +200,15 @@ int bl_attention_decode_tail(const void* q, const void* k_cache, const void* v_c
                              int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh, int page_size,
                              int window, float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate,
                              void* stream);
-// The `mma.sync` kernels with a cap c > 0 on the scaled scores as well, s <- c tanh(s / c), before the softmax (0: none).
+// The tcgen05 prompt kernel and the `mma.sync` kernels with a cap c > 0 on the scaled scores as well, s <- c tanh(s / c), before the softmax (0: none).
 int bl_attention_prefill_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                              const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
                              void* out, int H, int KV, int dh, int page_size, int window, float scale,
                              const void* sinks, int sink_dtype, const float* gate, int ld_gate, float softcap, void* stream);
+int bl_attention_prefill_tc_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
+                                void* out, int T, int n_pages, int H, int KV, int dh, int page_size, int window, float scale,
+                                const void* sinks, int sink_dtype, const float* gate, int ld_gate, float softcap, void* stream);
 int bl_attention_decode_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                             const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
                             int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh, int page_size,

@@ -76,6 +76,7 @@ struct Params {
     const int* tiles;                  // [n][2] (request, first token of the 128-row tile within the request)
     int H, KV, window; float scale_log2;
     BlAttnTail tail;                   // a sink per head and a gate per (token, head), or nulls
+    float cap_log2;                    // the kernel with a cap on the scores: the cap times log2 e (s <- cap tanh(s / cap) on the scaled score)
 };
 
 // Bounded wait. False when the bound ran out or another thread of the block has given up. SLEEP: the waiter is one
@@ -178,7 +179,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <class S>
+template <class S, bool CAP = false>
 __global__ void __launch_bounds__(S::THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -437,8 +438,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tmem_ld_wait(sa); tmem_ld32(t_s + (2 * cp + 1) * 32, sb); chunk_max(sa, 2 * cp);
                 tmem_ld_wait(sb); tmem_ld32(t_s + 64, sa); chunk_max(sb, 2 * cp + 1);   // chunk 2: next here, first of the second pass
             }
-            // the scale is positive: the maximum of the scaled scores is the scaled maximum
-            const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
+            // the scale is positive: the maximum of the scaled scores is the scaled maximum (and the cap is monotonic: the
+            // capped maximum is the cap of the maximum, so the first pass stays on raw scores)
+            const float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // tanh(y) = 1 - 2 / (1 + 2^(2 y log2 e)), y = raw * scale / cap
+            const float cap_x = CAP ? p.scale_log2 / p.cap_log2 * 2.8853900817779268f : 0.f;
+            float m_blk = m_raw * p.scale_log2;
+            if constexpr (CAP)
+                m_blk = m_raw == -INFINITY ? -INFINITY : p.cap_log2 * (1.0f - __fdividef(2.0f, 1.0f + bl_ex2(m_raw * cap_x)));
+            const float m_new = fmaxf(m, m_blk);
             float alpha = 1.f;
             // (a row's first keys: -inf + RESCALE is -inf, below any score; a row without keys so far stays as it is)
             if (__any_sync(0xffffffffu, m_new > m + RESCALE)) {
@@ -469,13 +477,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // Second pass, chunks 3 (still in sb), 2, 1, 0: P = 2^(s * scale - m) as bfloat16 into tensor memory, the A
             // operand of the second product: lane = row, two keys to a 32-bit column, 16 columns a chunk.
             auto chunk_exp = [&](uint32_t (&s)[32], int c) {
+                float x[32];
+                if constexpr (CAP) {
+                    // the cap in front of the mask (tanh of a masked minus infinity is finite; a chunk that the first pass
+                    // masked in place gives -1 here and is masked again by position)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float th = 1.0f - __fdividef(2.0f, 1.0f + bl_ex2(__uint_as_float(s[j]) * cap_x));
+                        x[j] = fmaf(th, p.cap_log2, -m_use);
+                    }
+                    if (!all_seen) {
+                        const int hi_c = hi_l - c * 32, lo_c = lo_l - c * 32;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) x[j] = (j <= hi_c && j > lo_c) ? x[j] : -INFINITY;
+                    }
+                } else {
                 if (!all_seen) mask(s, c);
                 // in batches, so that the special-function unit's queue stays full: 32 scaled differences, 32 x 2^x
                 // back to back (volatile keeps them together), then the sums and the pairs
-                float x[32];
 #pragma unroll
                 for (int j = 0; j < 32; j += 2)
                     f2_unpack(f2_fma(f2_pack(__uint_as_float(s[j]), __uint_as_float(s[j + 1])), scale2, minus_m2), x[j], x[j + 1]);
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+f"(x[j]));
                 uint32_t pk[16];
@@ -597,7 +620,7 @@ extern "C" int bl_attention_prefill_tc_supported(int dh, int page_size) { return
 
 namespace {
 
-template <class S>
+template <class S, bool CAP>
 int launch(const void* q, const void* k_cache, const void* v_cache, const Params& p, int n_tiles, int T, int n_pages, cudaStream_t stream) {
     CUtensorMap mq, mk, mv;
     if (bl_make_map_bf16(WHO, &mq, q, T, p.H * S::DH, ROWS, 64)) return 1;
@@ -605,12 +628,12 @@ int launch(const void* q, const void* k_cache, const void* v_cache, const Params
     if (bl_make_map_bf16(WHO, &mv, v_cache, (long long)n_pages * p.KV * PAGE, S::DH, PAGE, 64)) return 1;
     static bool configured = false;                                      // per shape
     if (!configured) {
-        BL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES));
+        BL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<S, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES));
         configured = true;
     }
     // A block waits (griddepcontrol.wait) before it allocates tensor memory or touches data, so it may be launched
     // while the kernel before it still runs.
-    BL_CUDA(bl_launch_dependent(attention_tc_kernel<S>, dim3(n_tiles * p.H, 1, 1), dim3(S::THREADS), (size_t)S::SMEM_BYTES, stream,
+    BL_CUDA(bl_launch_dependent(attention_tc_kernel<S, CAP>, dim3(n_tiles * p.H, 1, 1), dim3(S::THREADS), (size_t)S::SMEM_BYTES, stream,
                                 mq, mk, mv, p));
     BL_CHECK_LAUNCH("bl_attention_prefill_tc");
     return 0;
@@ -633,7 +656,18 @@ extern "C" int bl_attention_prefill_tc_tail(const void* q, const void* k_cache, 
                                             int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,
                                             int window, float scale, const void* sinks, int sink_dtype, const float* gate,
                                             int ld_gate, void* stream) {
+    return bl_attention_prefill_tc_cap(q, k_cache, v_cache, cu_q, ctx_len, block_table, max_pages, tiles, n_tiles, out, T, n_pages, H, KV,
+                                       dh, page_size, window, scale, sinks, sink_dtype, gate, ld_gate, 0.f, stream);
+}
+
+// ... and a cap c > 0 on the scaled scores, s <- c tanh(s / c), before the softmax (0: none; the kernel without it).
+extern "C" int bl_attention_prefill_tc_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
+                                           const int* ctx_len, const int* block_table, int max_pages, const int* tiles,
+                                           int n_tiles, void* out, int T, int n_pages, int H, int KV, int dh, int page_size,
+                                           int window, float scale, const void* sinks, int sink_dtype, const float* gate,
+                                           int ld_gate, float softcap, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (!(softcap >= 0.f)) BL_FAIL("bl_attention_prefill_tc: a cap on the scores must not be negative, got %g", (double)softcap);
     if ((dh != 64 && dh != 128) || page_size != PAGE)
         BL_FAIL("bl_attention_prefill_tc: head size %d with pages of %d tokens is not built (64 or 128 with 16 only)", dh, page_size);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("bl_attention_prefill_tc: %d heads cannot share %d key/value heads", H, KV);
@@ -646,8 +680,13 @@ extern "C" int bl_attention_prefill_tc_tail(const void* q, const void* k_cache, 
     p.out = (__nv_bfloat16*)out; p.cu_q = cu_q; p.ctx_len = ctx_len; p.block_table = block_table; p.max_pages = max_pages;
     p.tiles = tiles; p.H = H; p.KV = KV; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
-    if (dh == 64) return launch<Shape<64, 2>>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
-    return launch<Shape<128, 1>>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
+    p.cap_log2 = softcap * 1.4426950408889634f;
+    if (softcap > 0.f) {
+        if (dh == 64) return launch<Shape<64, 2>, true>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
+        return launch<Shape<128, 1>, true>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
+    }
+    if (dh == 64) return launch<Shape<64, 2>, false>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
+    return launch<Shape<128, 1>, false>(q, k_cache, v_cache, p, n_tiles, T, n_pages, (cudaStream_t)stream);
 }
 
 // Reads and clears the status word: 0 when no block has given up on a wait since the last call. Codes name the

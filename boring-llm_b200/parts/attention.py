@@ -74,7 +74,7 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
     Otherwise, and always in float32, the plain kernel. Which requests those are comes from the step's plan
     (`attention_plan`). `sinks` [H] and `gate` (32-bit logits [T, >= H]) are what may follow the softmax: a score per
     head that joins the denominator, a sigmoid per (token, head) on the output. `softcap` c > 0: scaled scores pass
-    c tanh(s / c) before the softmax (the plain and the `mma.sync` kernels have it)."""
+    c tanh(s / c) before the softmax (the plain, the `mma.sync` and the tcgen05 prompt kernels have it)."""
     dv = v_cache.shape[3]
     if not (ctx.fast and dv == dh and ops.attention_mma_supported(q.dtype, dh, k_cache.shape[2])):
         ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, H, window, scale, sinks, gate,
@@ -87,8 +87,9 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
         ctx.plans[PLAN_KEY] = plan
     tiles64, tiles128, singles = plan.arrays["tiles64"], plan.arrays["tiles128"], plan.arrays["singles"]
     if tiles64.shape[0]:
-        if tiles128.shape[0] and softcap == 0.0 and ops.attention_prefill_tc_supported(q.dtype, dh, k_cache.shape[2]):
-            ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles128, out, H, window, scale, sinks, gate)
+        if tiles128.shape[0] and ops.attention_prefill_tc_supported(q.dtype, dh, k_cache.shape[2]):
+            ops.attention_prefill_tc(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles128, out, H, window, scale, sinks, gate,
+                                     softcap=softcap)
         else:
             ops.attention_prefill(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, tiles64, out, H, window, scale, sinks, gate,
                                   softcap=softcap)

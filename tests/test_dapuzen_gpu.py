@@ -411,8 +411,9 @@ def test_capped_attention_kernel_with_planted_keys(H, G, dk, dv, window, cap):
 
 @pytest.mark.parametrize("dh,H,G,window,cap", [(64, 4, 2, 0, 3.0), (32, 2, 2, 40, 1.5), (96, 4, 1, 150, 6.0), (128, 2, 1, 0, 2.0)])
 def test_capped_scores_in_the_tensor_core_attention_kernels(dh, H, G, window, cap):
-    """The bfloat16 `mma.sync` kernels (prompt tiles; single tokens in one slice, in a cluster's slices, merged through
-    scratch) with a cap well below the raw scores' spread, so that a kernel without the cap gives visibly other rows."""
+    """The bfloat16 tensor-core kernels (prompt tiles on `mma.sync` and, at head sizes 64 and 128, on tcgen05; single tokens
+    in one slice, in a cluster's slices, merged through scratch) with a cap well below the raw scores' spread, so that a
+    kernel without the cap gives visibly other rows."""
     from boring_llm_b200.kernels import ops
     from boring_llm_b200.parts.attention import attention_plan
     T, page = 300, 16
@@ -433,6 +434,11 @@ def test_capped_scores_in_the_tensor_core_attention_kernels(dh, H, G, window, ca
     out = torch.zeros(T, H * dh, dtype=torch.bfloat16, device=DEV)
     ops.attention_prefill(qg, kc, vc, i32([0, T]), i32([T]), tb, i32(plan.arrays["tiles64"]), out, H, window, scale, softcap=cap)
     np.testing.assert_allclose(out.float().cpu().numpy(), want.numpy(), **tol)
+    if ops.attention_prefill_tc_supported(torch.bfloat16, dh, page):
+        out = torch.zeros(T, H * dh, dtype=torch.bfloat16, device=DEV)
+        ops.attention_prefill_tc(qg, kc, vc, i32([0, T]), i32([T]), tb, i32(plan.arrays["tiles128"]), out, H, window, scale, softcap=cap)
+        ops.check_status()
+        np.testing.assert_allclose(out.float().cpu().numpy(), want.numpy(), err_msg="tcgen05", **tol)
     ctxs = [300, 170, 33]
     rows = [c - 1 for c in ctxs]
     qd = qg[rows].contiguous()
