@@ -200,7 +200,7 @@ int bl_attention_decode_tail(const void* q, const void* k_cache, const void* v_c
                              int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh, int page_size,
                              int window, float scale, const void* sinks, int sink_dtype, const float* gate, int ld_gate,
                              void* stream);
-// The tcgen05 prompt kernel and the `mma.sync` kernels with a cap c > 0 on the scaled scores as well, s <- c tanh(s / c), before the softmax (0: none).
+// The tcgen05 prompt kernel, the TMA-fed decode kernel and the `mma.sync` kernels with a cap c > 0 on the scaled scores as well, s <- c tanh(s / c), before the softmax (0: none).
 int bl_attention_prefill_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                              const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
                              void* out, int H, int KV, int dh, int page_size, int window, float scale,
@@ -209,6 +209,11 @@ int bl_attention_prefill_tc_cap(const void* q, const void* k_cache, const void* 
                                 const int* ctx_len, const int* block_table, int max_pages, const int* tiles, int n_tiles,
                                 void* out, int T, int n_pages, int H, int KV, int dh, int page_size, int window, float scale,
                                 const void* sinks, int sink_dtype, const float* gate, int ld_gate, float softcap, void* stream);
+int bl_attention_decode_tma_cap(const void* q, const void* k_cache, const void* v_cache, int n_pages, const int* cu_q,
+                                const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                int n_splits, void* out, int H, int KV, int dh, int page_size, int window, float scale,
+                                int early, const void* sinks, int sink_dtype, const float* gate, int ld_gate, float softcap,
+                                void* stream);
 int bl_attention_decode_cap(const void* q, const void* k_cache, const void* v_cache, const int* cu_q,
                             const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
                             int n_splits, float* scratch, int* counters, void* out, int H, int KV, int dh, int page_size,

@@ -75,6 +75,7 @@ struct Params {
     const int* reqs; int n_splits;
     int H, KV, window; float scale_log2;
     BlAttnTail tail;              // a sink per head and a gate per (token, head), or nulls
+    float cap_log2;               // > 0: a cap c on the scaled scores, s <- c tanh(s / c), here times log2 e (0: none)
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -141,10 +142,11 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, int 
 
 // One unit of 32 keys: scores, running maximum, 2^x, and the product with the values. NH: n-tiles of 8 heads.
 // EDGE: some of the unit's keys lie outside [lo, hi] (their rows of V are zero already).
-template <int DH, int NH, bool EDGE>
+template <int DH, int NH, bool EDGE, bool CAP>
 __device__ __forceinline__ void unit_step(uint32_t stage, const uint32_t (&koff)[4], const uint32_t (&voff)[4],
                                           const unsigned (&qb)[NH][DH / 16][2], float (&o)[NH][DH / 16][4],
-                                          float (&m)[NH][2], float (&l)[NH][2], int k0, int lo, int hi, float scale_log2) {
+                                          float (&m)[NH][2], float (&l)[NH][2], int k0, int lo, int hi, float scale_log2,
+                                          float cap_log2) {
     using S = Shape<DH>;
     const int g = (threadIdx.x & 31) >> 2;
     float s[2][NH][4];
@@ -158,6 +160,20 @@ __device__ __forceinline__ void unit_step(uint32_t stage, const uint32_t (&koff)
             ldmatrix_x4(a, stage + (kk >> 2) * S::ATOM_BYTES + mt * (16 * 128) + koff[kk & 3]);
 #pragma unroll
             for (int nh = 0; nh < NH; ++nh) mma_bf16(s[mt][nh], a, qb[nh][kk][0], qb[nh][kk][1]);
+        }
+    }
+    if constexpr (CAP) {
+        // a cap on the scores: raw r becomes tanh(r a) / a, a = scale / cap, so that the scaled score is cap tanh(r scale / cap);
+        // monotonic (the maximum of the raw scores still gives the scaled maximum), and in front of the mask (tanh of minus
+        // infinity is finite). tanh(x) = 1 - 2 / (1 + 2^(2 x log2 e)).
+        const float ax = scale_log2 / cap_log2 * 2.8853900817779268f, ia = cap_log2 / scale_log2;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) s[mt][nh][c] = (1.0f - __fdividef(2.0f, 1.0f + ex2(s[mt][nh][c] * ax))) * ia;
+            }
         }
     }
     if (EDGE) {
@@ -231,7 +247,7 @@ __device__ __forceinline__ void unit_step(uint32_t stage, const uint32_t (&koff)
     }
 }
 
-template <int DH, int NH>
+template <int DH, int NH, bool CAP = false>
 __global__ void __launch_bounds__(THREADS)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const Params p) {
     using S = Shape<DH>;
@@ -348,10 +364,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     *reinterpret_cast<uint32_t*>(gen + (stage - base) + S::TENSOR_BYTES + a * S::ATOM_BYTES + row * 128 + lane * 4) = 0u;
             }
             __syncwarp();
-            unit_step<DH, NH, true>(stage, koff, voff, qb, o, m, l, k0, lo, hi, p.scale_log2);
+            unit_step<DH, NH, true, CAP>(stage, koff, voff, qb, o, m, l, k0, lo, hi, p.scale_log2, p.cap_log2);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeros were plain stores; the stage's next filling is a TMA copy
         } else {
-            unit_step<DH, NH, false>(stage, koff, voff, qb, o, m, l, k0, lo, hi, p.scale_log2);
+            unit_step<DH, NH, false, CAP>(stage, koff, voff, qb, o, m, l, k0, lo, hi, p.scale_log2, p.cap_log2);
         }
         __syncwarp();                                             // every lane has read the stage
         if (issued < n_mine) {                                    // the stage just used takes the unit STAGES on
@@ -447,15 +463,15 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     cluster_sync_all();                                           // nobody leaves while a store to its shared memory may be in flight
 }
 
-template <int DH, int NH>
+template <int DH, int NH, bool CAP = false>
 int configure(int* smem_bytes) {
     static bool done = false;
     *smem_bytes = Shape<DH>::SMEM_BYTES;
     if (!done) {
-        BL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<DH, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DH>::SMEM_BYTES));
-        BL_CUDA(bl_same_carveout(attention_decode_kernel<DH, NH>));
+        BL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<DH, NH, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<DH>::SMEM_BYTES));
+        BL_CUDA(bl_same_carveout(attention_decode_kernel<DH, NH, CAP>));
         // clusters of more than 8 blocks need the kernel's consent; a device that refuses it keeps 8
-        if (cudaFuncSetAttribute(attention_decode_kernel<DH, NH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_decode_kernel<DH, NH, CAP>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
             (void)cudaGetLastError();
         done = true;
     }
@@ -466,10 +482,10 @@ int configure(int* smem_bytes) {
 // its copies of the cached keys and values under the predecessor's tail. Large clusters of a launch with more blocks
 // than SMs are better launched late: placed while the predecessor's blocks still hold SMs, they pile up two to an SM
 // beside SMs that stay empty, and a long context then runs at the pace of the doubly loaded SMs.
-template <int DH, int NH>
+template <int DH, int NH, bool CAP = false>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, dim3 grid, bool early, cudaStream_t s) {
     int bytes = 0;
-    if (configure<DH, NH>(&bytes)) return 1;
+    if (configure<DH, NH, CAP>(&bytes)) return 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = (size_t)bytes; cfg.stream = s;
     cudaLaunchAttribute attr[2];
@@ -478,7 +494,7 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, dim3 g
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = p.n_splits; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = p.n_splits > 1 ? 2 : 1;
-    BL_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_kernel<DH, NH>, mk, mv, p));
+    BL_CUDA(cudaLaunchKernelEx(&cfg, attention_decode_kernel<DH, NH, CAP>, mk, mv, p));
     BL_CHECK_LAUNCH(WHO);
     return 0;
 }
@@ -546,7 +562,18 @@ extern "C" int bl_attention_decode_tma_tail(const void* q, const void* k_cache, 
                                             int n_splits, void* out, int H, int KV, int dh, int page_size, int window,
                                             float scale, int early, const void* sinks, int sink_dtype, const float* gate,
                                             int ld_gate, void* stream) {
+    return bl_attention_decode_tma_cap(q, k_cache, v_cache, n_pages, cu_q, ctx_len, block_table, max_pages, reqs, n, n_splits, out, H, KV,
+                                       dh, page_size, window, scale, early, sinks, sink_dtype, gate, ld_gate, 0.f, stream);
+}
+
+// ... and a cap c > 0 on the scaled scores, s <- c tanh(s / c), before the softmax (0: none).
+extern "C" int bl_attention_decode_tma_cap(const void* q, const void* k_cache, const void* v_cache, int n_pages, const int* cu_q,
+                                           const int* ctx_len, const int* block_table, int max_pages, const int* reqs, int n,
+                                           int n_splits, void* out, int H, int KV, int dh, int page_size, int window,
+                                           float scale, int early, const void* sinks, int sink_dtype, const float* gate,
+                                           int ld_gate, float softcap, void* stream) {
     if (n <= 0) return 0;
+    if (!(softcap >= 0.f)) BL_FAIL("%s: a cap on the scores must not be negative, got %g", WHO, (double)softcap);
     if (!(scale > 0.f)) BL_FAIL("%s: the scale of the scores must be positive (got %g)", WHO, (double)scale);
     if (H <= 0 || KV <= 0 || H % KV != 0) BL_FAIL("%s: %d heads cannot share %d key/value heads", WHO, H, KV);
     if (!built(dh, page_size)) BL_FAIL("%s: head size %d with pages of %d is not built (64 or 128, pages of 16)", WHO, dh, page_size);
@@ -558,6 +585,7 @@ extern "C" int bl_attention_decode_tma_tail(const void* q, const void* k_cache, 
     p.block_table = block_table; p.max_pages = max_pages; p.reqs = reqs; p.n_splits = n_splits;
     p.H = H; p.KV = KV; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
     p.tail = BlAttnTail{sinks, sink_dtype, gate, ld_gate};
+    p.cap_log2 = softcap * 1.4426950408889634f;
     CUtensorMap mk, mv;
     if (bl_make_map_bf16(WHO, &mk, k_cache, (long long)n_pages * KV * PAGE, dh, PAGE, 64)) return 1;
     if (bl_make_map_bf16(WHO, &mv, v_cache, (long long)n_pages * KV * PAGE, dh, PAGE, 64)) return 1;
@@ -565,6 +593,10 @@ extern "C" int bl_attention_decode_tma_tail(const void* q, const void* k_cache, 
     const bool two = G > 8;
     const dim3 grid(n_splits, KV * ((G + (two ? 16 : 8) - 1) / (two ? 16 : 8)), n);
     cudaStream_t s = (cudaStream_t)stream;
+    if (softcap > 0.f) {                                          // a second build of the kernel: without a cap it is the code it was
+        if (dh == 64) return two ? launch<64, 2, true>(mk, mv, p, grid, early != 0, s) : launch<64, 1, true>(mk, mv, p, grid, early != 0, s);
+        return two ? launch<128, 2, true>(mk, mv, p, grid, early != 0, s) : launch<128, 1, true>(mk, mv, p, grid, early != 0, s);
+    }
     if (dh == 64) return two ? launch<64, 2>(mk, mv, p, grid, early != 0, s) : launch<64, 1>(mk, mv, p, grid, early != 0, s);
     return two ? launch<128, 2>(mk, mv, p, grid, early != 0, s) : launch<128, 1>(mk, mv, p, grid, early != 0, s);
 }

@@ -456,7 +456,8 @@ def attention_decode_tma_supported(dtype: torch.dtype, dh: int, page_size: int) 
 
 
 def attention_decode_tma(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, n_splits: int, out, H: int, window: int,
-                         scale: float, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                         scale: float, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                         softcap: float = 0.0) -> None:
     """`attention_decode` for head sizes 64 and 128 with keys and values streamed by TMA into per-warp rings and the
     query heads of a key/value head as the columns of the MMAs; 1 to `DECODE_CLUSTER_SPLITS` slices, which are the
     blocks of one cluster and send their partial rows to the blocks that finish them."""
@@ -473,7 +474,11 @@ def attention_decode_tma(q, k_cache, v_cache, cu_q, ctx_len, block_table, reqs, 
     G = H // KV
     blocks = n * KV * (-(-G // (8 if G <= 8 else 16))) * n_splits
     early = not (n_splits >= DECODE_TMA_LATE_CLUSTER and blocks > _sms())
-    if sinks is None and gate is None:
+    if softcap > 0:                          # a cap on the scaled scores: a second build of the kernel
+        _call(_lib().bl_attention_decode_tma_cap, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
+          block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale),
+          1 if early else 0, *_tail(T, H, sinks, gate), ctypes.c_float(softcap), _stream())
+    elif sinks is None and gate is None:
         _call(_lib().bl_attention_decode_tma, _p(q), _p(k_cache), _p(v_cache), n_pages, _p(cu_q), _p(ctx_len), _p(block_table),
           block_table.shape[1], _p(reqs), n, n_splits, _p(out), H, KV, dh, page_size, window, ctypes.c_float(scale),
           1 if early else 0, _stream())

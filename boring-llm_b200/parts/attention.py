@@ -74,7 +74,7 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
     Otherwise, and always in float32, the plain kernel. Which requests those are comes from the step's plan
     (`attention_plan`). `sinks` [H] and `gate` (32-bit logits [T, >= H]) are what may follow the softmax: a score per
     head that joins the denominator, a sigmoid per (token, head) on the output. `softcap` c > 0: scaled scores pass
-    c tanh(s / c) before the softmax (the plain, the `mma.sync` and the tcgen05 prompt kernels have it)."""
+    c tanh(s / c) before the softmax (every attention kernel has it)."""
     dv = v_cache.shape[3]
     if not (ctx.fast and dv == dh and ops.attention_mma_supported(q.dtype, dh, k_cache.shape[2])):
         ops.attention_plain(q, k_cache, v_cache, ctx.tok_req, ctx.cu_q, ctx.ctx_len, table, out, H, window, scale, sinks, gate,
@@ -100,11 +100,11 @@ def paged_attention(ctx, q, k_cache, v_cache, table, out, H: int, KV: int, dh: i
         if window > 0:
             longest = min(longest, window + 64)
         G = H // KV
-        if softcap == 0.0 and ops.attention_decode_tma_supported(q.dtype, dh, k_cache.shape[2]):
+        if ops.attention_decode_tma_supported(q.dtype, dh, k_cache.shape[2]):
             # head sizes 64 and 128: the TMA-fed kernel, which knows how many slices pay for this many requests
             n_splits = ops.attention_decode_tma_splits(n, KV, G, dh, longest)
             ops.attention_decode_tma(q, k_cache, v_cache, ctx.cu_q, ctx.ctx_len, table, singles, n_splits, out, H, window, scale,
-                                     sinks, gate)
+                                     sinks, gate, softcap=softcap)
             return
         groups = KV * (-(-G // 16))
         resident = ops.attention_decode_resident_blocks(dh)

@@ -412,7 +412,7 @@ def test_capped_attention_kernel_with_planted_keys(H, G, dk, dv, window, cap):
 @pytest.mark.parametrize("dh,H,G,window,cap", [(64, 4, 2, 0, 3.0), (32, 2, 2, 40, 1.5), (96, 4, 1, 150, 6.0), (128, 2, 1, 0, 2.0)])
 def test_capped_scores_in_the_tensor_core_attention_kernels(dh, H, G, window, cap):
     """The bfloat16 tensor-core kernels (prompt tiles on `mma.sync` and, at head sizes 64 and 128, on tcgen05; single tokens
-    in one slice, in a cluster's slices, merged through scratch) with a cap well below the raw scores' spread, so that a
+    in one slice, in a cluster's slices, merged through scratch, and fed by TMA) with a cap well below the raw scores' spread, so that a
     kernel without the cap gives visibly other rows."""
     from boring_llm_b200.kernels import ops
     from boring_llm_b200.parts.attention import attention_plan
@@ -448,6 +448,12 @@ def test_capped_scores_in_the_tensor_core_attention_kernels(dh, H, G, window, ca
         sc = torch.empty(ops.attention_decode_scratch(3, H, dh, splits), device=DEV) if scratch else None
         ops.attention_decode(qd, kc, vc, i32([0, 1, 2, 3]), i32(ctxs), tb3, i32([0, 1, 2]), splits, out, H, window, scale, sc, softcap=cap)
         np.testing.assert_allclose(out.float().cpu().numpy(), want[rows].numpy(), err_msg=f"decode, {splits} slices", **tol)
+    if ops.attention_decode_tma_supported(torch.bfloat16, dh, page):
+        for splits in (1, 3):
+            out = torch.zeros(3, H * dh, dtype=torch.bfloat16, device=DEV)
+            ops.attention_decode_tma(qd, kc, vc, i32([0, 1, 2, 3]), i32(ctxs), tb3, i32([0, 1, 2]), splits, out, H, window, scale, softcap=cap)
+            ops.check_status()
+            np.testing.assert_allclose(out.float().cpu().numpy(), want[rows].numpy(), err_msg=f"TMA decode, {splits} slices", **tol)
 
 
 def load_part(part, W, dtype):
