@@ -423,7 +423,7 @@ def miforax_config(sizes, n_layers):
 
 
 DAPUZEN_WINDOW = 1024
-DAPUZEN_PATTERN = ("parallel", "retention", "attention", "attention")     # repeated over the layers; the odd ones have experts
+DAPUZEN_PATTERN = ("attention", "parallel", "retention", "attention")     # repeated over the layers; the odd ones have experts
 DAPUZEN_EXPERTS, DAPUZEN_TOP, DAPUZEN_IDENTITY, DAPUZEN_GROUPS, DAPUZEN_KEEP = 14, 4, 2, 2, 1
 DAPUZEN_STATE = 128
 
@@ -432,7 +432,7 @@ def dapuzen_config(sizes, n_layers):
     """A Dapuzen model with the width, heads, head size, layers and vocabulary of a Qwen2.5 size: the attention mixers have
     the Qwen2 heads and windows of 1,024 (the parallel layer's with capped scores and biases, beside a state-space mixer of
     width / head size heads over a state of 128 in two groups); retention has half the heads with values twice as wide;
-    every second layer has the dense feed-forward with xIELU, the others 14 experts of a quarter of its hidden size and 2
+    the even layers have the dense feed-forward with xIELU, the odd ones 14 experts of a quarter of its hidden size and 2
     identity experts, 4 a token from the better of 2 groups, beside a gated shared expert of half of it."""
     import boring_llm_b200 as b
     s = SIZES[sizes]
@@ -448,7 +448,7 @@ def dapuzen_config(sizes, n_layers):
         "retention": {"heads": Hr, "dim": dh, "vdim": 2 * dh, "decay": [1.0 - 2.0 ** (-5 - 3 * i / max(1, Hr - 1)) for i in range(Hr)],
                       "rot": {"base": 1000000.0, "dims": dh}},
         "parallel": {"left": left, "right": {"heads": d // dh, "vdim": dh, "state": DAPUZEN_STATE, "groups": 2, "conv": 4, "norm_groups": 2},
-                     "left_scale": 0.8, "right_scale": 0.5},
+                     "left_scale": 0.7, "right_scale": 0.6},
     }
     moe = {"kind": "moe", "expert": {"ff": F // 4 // 8 * 8},
            "router": {"experts": DAPUZEN_EXPERTS, "top": DAPUZEN_TOP, "identity": DAPUZEN_IDENTITY,

@@ -66,7 +66,7 @@ def _feed_forward(cfg: DapuzenConfig, f, p: str):
         if not f.shared_ff:
             return experts
         shared = GluMLP(d, f.shared_ff, {"w_gate": p + "shared.gate", "w_up": p + "shared.up", "w_down": p + "shared.down"})
-        return SumFeedForward([experts, RowGatedFeedForward(d, shared, {"gate": p + "shared.sg"})])
+        return SumFeedForward([experts, RowGatedFeedForward(d, shared, {"gate": p + "shared.sg"}, logit_from=experts)])
     raise TypeError(f"no feed-forward for {type(f).__name__}")
 
 

@@ -221,12 +221,15 @@ class SumFeedForward(FeedForward):
 
 class RowGatedFeedForward(FeedForward):
     """A feed-forward whose result is multiplied by sigmoid(w . h), ONE number per token (`gate` [1, dim]), before it joins
-    the stream: x += sigmoid(h gate^T) * inner(h). The gate's logit is 32-bit."""
+    the stream: x += sigmoid(h gate^T) * inner(h). The gate's logit is 32-bit. `logit_from`: a part that runs BEFORE this one
+    on the same rows and begins with a product of them (`join_rows`, `joined_out`: routed experts' router): the gate's row
+    becomes one more row of that product's matrix, and the logit costs no launch of its own."""
 
-    def __init__(self, dim: int, inner: FeedForward, names: Dict[str, str]):
+    def __init__(self, dim: int, inner: FeedForward, names: Dict[str, str], logit_from=None):
         super().__init__(names)
-        self.dim, self.inner = dim, inner
+        self.dim, self.inner, self.logit_from = dim, inner, logit_from
         self.gate = None
+        self._joined = False
 
     def children(self):
         return (self.inner,)
@@ -238,13 +241,22 @@ class RowGatedFeedForward(FeedForward):
     def local_specs(self):
         return {"gate": TensorSpec((1, self.dim), MATRIX)}
 
+    def place(self, local, dtype, device):
+        self.gate = to_device_matrix(local["gate"], dtype, device)
+        src = self.logit_from
+        if src is not None and getattr(src, "router", None) is not None and hasattr(src, "join_rows"):
+            src.join_rows(self.gate)                     # (the other part's tensors are placed already: it comes first)
+            self._joined = True
+
     def forward(self, ctx, h, residual):
         after, ctx.next_norm = ctx.next_norm, None       # the inner result is not the stream: its product begins no norm
         y = ctx.empty(tuple(residual.shape), torch.float32)
         self.inner.apply(ctx, h, y)
         ctx.next_norm = after
-        logit = ctx.empty((h.shape[0], 1), torch.float32)
-        linear(ctx, h, self.gate, logit, None, EPI_NONE)
+        logit = self.logit_from.joined_out if self._joined else None
+        if logit is None or logit.shape[0] != h.shape[0]:
+            logit = ctx.empty((h.shape[0], 1), torch.float32)
+            linear(ctx, h, self.gate, logit, None, EPI_NONE)
         ops.add_row_gated(residual, y, logit)
 
 
@@ -285,7 +297,7 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"RoutedExperts: {top} experts a token out of {keep_groups} groups of {self.n_out // n_groups}")
         self.dim, self.hidden, self.E, self.top = dim, hidden, n_experts, top
         self.n_groups, self.keep_groups, self.has_correction = n_groups, keep_groups, bool(correction)
-        self.router = self.correction = self.w_gate_up = self.w_down = self.act_args = None
+        self.router = self.correction = self.w_gate_up = self.w_down = self.act_args = self.joined_out = None
         self.record = None               # a list: every step appends a copy of the experts it chose [T, top] (tests; kernels launched singly)
 
     def choice_specs(self):
@@ -315,11 +327,23 @@ class RoutedExperts(FeedForward):
         self.w_down = to_device_matrix(torch.stack([local[f"down{e}"] for e in range(self.E)]), dtype, device)
         self.act_args = ops.glu_args(GluMLP.KINDS[self.activation], self.limit, device)
 
+    def join_rows(self, weight) -> None:
+        """Further rows for the router's matrix, from a part that reads the same rows (a gate of one number per token on
+        another feed-forward); after each run their 32-bit sums are `self.joined_out` [T, rows]."""
+        pad = -self.router.shape[0] % 8          # the further columns start on a 32-byte boundary of the 32-bit sums
+        self.n_own = self.router.shape[0] + pad
+        self.router = torch.cat([self.router, self.router.new_zeros((pad, self.router.shape[1])),
+                                 weight.to(device=self.router.device, dtype=self.router.dtype)], dim=0).contiguous()
+
     def route(self, ctx, h):
         """(experts [T, top] int32, weights [T, top] 32-bit) of the rows h."""
         T = h.shape[0]
-        z = ctx.empty((T, self.n_out), torch.float32)
+        z = ctx.empty((T, self.router.shape[0]), torch.float32)
         linear(ctx, h, self.router, z, None, EPI_NONE)            # 32-bit sums of exact products (the rows may be bfloat16 roundings)
+        n_own = getattr(self, "n_own", None)
+        self.joined_out = z[:, n_own:] if n_own is not None else None
+        if n_own is not None:
+            z = z[:, :self.n_out]
         ids = torch.empty((T, self.top), dtype=torch.int32, device=ctx.device)
         wts = ctx.empty((T, self.top), torch.float32)
         ops.moe_route(z, self.correction, self.top, self.n_groups, self.keep_groups, ids, wts, self.score, self.group_top)

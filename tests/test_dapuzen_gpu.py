@@ -79,7 +79,7 @@ SHAPES = {
     # every mixer and feed-forward; windows that are no multiple of the page; values wider than keys; partial rotation;
     # groups of two over experts and identity experts together; layers that run with another's tensors; a layer without
     # feed-forward
-    "A": model(97, 64, 1e-5, 3.0, [
+    "A": model(97, 64, 1e-5, 2.5, [
         layer("parallel", _PA, dense(48)), layer("retention", _RA, _MA), layer("attention", _AA),
         layer("parallel", _PA, dense(48), weights_of=0), layer("attention", _AA, weights_of=2),
         layer("retention", _RA, _MA, weights_of=1),
@@ -97,7 +97,7 @@ SHAPES = {
     "C": model(300, 128, 1e-6, 11.3, [
         layer("parallel", par(att(4, 2, 64, 64, 150, 0.11), ssd(4, 32, 64, 2, 4, 2), 0.8, 0.6, 30.0), dense(256)),
         layer("attention", att(6, 2, 64, 64, 70, 0.12, base=500000.0, dims=32), moe(64, 8, 3, identity=2, groups=2, keep=1, shared=96)),
-        layer("retention", ret(2, 64, 64, [0.96875, 0.998], base=1e6), dense(192))]),
+        layer("retention", ret(2, 64, 64, [0.95, 0.998], base=5e5), dense(192))]),
 }
 SEEDS = {"A": 41, "B": 42, "C": 43}
 BF16_TOL = 6e-2
